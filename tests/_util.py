@@ -1,0 +1,35 @@
+"""Shared helpers for the tests: fixture loading and tolerance bookkeeping."""
+import glob
+import os
+
+import numpy as np
+import torch
+
+from attention_oracle import INPUT_NAMES, OUTPUT_NAMES
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def golden_case_names():
+    names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+    return [n for n in names if n != "config1_head"]
+
+
+def load_golden(name):
+    """Returns (meta dict, inputs dict of bf16 tensors, outputs dict of fp32 tensors, mask)."""
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    B, H, N_q, N_kv, D, ws, cid, seed = (int(x) for x in z["meta"])
+    meta = dict(B=B, H=H, N_q=N_q, N_kv=N_kv, D=D, window_size=ws, chunk_id=cid, seed=seed)
+    inp = {n: torch.from_numpy(z["in_" + n].view(np.int16).copy()).view(torch.bfloat16)
+           for n in INPUT_NAMES}
+    out = {n: torch.from_numpy(z["out_" + n]) for n in OUTPUT_NAMES}
+    return meta, inp, out, torch.from_numpy(z["mask"])
+
+
+def load_config1_head():
+    z = np.load(os.path.join(GOLDEN_DIR, "config1_head.npz"))
+    inp = {n: torch.from_numpy(z["in_" + n]) for n in INPUT_NAMES}
+    out = {n: torch.from_numpy(z["out_" + n]) for n in OUTPUT_NAMES}
+    norms = {n: float(z["norm_" + n]) for n in OUTPUT_NAMES}
+    sums = {n: float(z["sum_" + n]) for n in OUTPUT_NAMES}
+    return tuple(int(x) for x in z["head"]), inp, out, norms, sums
