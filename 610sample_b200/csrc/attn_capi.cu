@@ -1,0 +1,221 @@
+// C ABI of libattn_b200.so (see include/attn_b200.h): argument checks, geometry,
+// kernel-family dispatch, per-thread error text and the device status word.
+#include "attn_b200.h"
+#include "attn_launch.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace {
+
+thread_local char tl_error[512] = "";
+thread_local int tl_launches = 0;
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// One status word per device, in device global memory owned by this library.
+__device__ unsigned int g_status_word = 0u;
+
+constexpr int kMaxDevices = 64;
+unsigned int* g_status_ptr[kMaxDevices] = {nullptr};
+std::mutex g_status_mutex;
+
+int status_pointer(unsigned int** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ATTN_EINVAL, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (g_status_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_status_word);
+    if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_status_ptr[dev] = static_cast<unsigned int*>(p);
+  }
+  *out = g_status_ptr[dev];
+  return ATTN_OK;
+}
+
+int check_shape(const attn_shape_t* s) {
+  if (s == nullptr) return fail(ATTN_EINVAL, "shape is null");
+  if (s->B < 0 || s->H < 0 || s->N_q < 0 || s->N_kv < 0) return fail(ATTN_EINVAL, "negative size");
+  if (s->dtype != ATTN_F16 && s->dtype != ATTN_BF16 && s->dtype != ATTN_F32)
+    return fail(ATTN_EUNSUPPORTED, "dtype %d: expected ATTN_F16, ATTN_BF16 or ATTN_F32", s->dtype);
+  if (s->D <= 0 || s->D % 16 != 0) return fail(ATTN_EINVAL, "D must be a positive multiple of 16 (got %d)", s->D);
+  if (s->D > 128) return fail(ATTN_EUNSUPPORTED, "unsupported head dimension D=%d (maximum 128)", s->D);
+  if (s->mask_mode != ATTN_MASK_REFERENCE && s->mask_mode != ATTN_MASK_NONE)
+    return fail(ATTN_EINVAL, "mask_mode %d unknown", s->mask_mode);
+  if (s->window_size < 0) return fail(ATTN_EINVAL, "window_size must be >= 0");
+  if (s->chunk_id < 0) return fail(ATTN_EINVAL, "chunk_id must be >= 0");
+  if ((long long)s->chunk_id * s->N_q + s->N_q > (1LL << 30)) return fail(ATTN_EINVAL, "chunk_id * N_q too large");
+  if ((long long)s->B * s->H > (1LL << 24)) return fail(ATTN_EINVAL, "B * H too large");
+  if (s->impl < ATTN_IMPL_AUTO || s->impl > ATTN_IMPL_TENSOR) return fail(ATTN_EINVAL, "impl %d unknown", s->impl);
+  if (s->impl == ATTN_IMPL_TENSOR && !attn::tc_supported(s->dtype, s->D))
+    return fail(ATTN_EUNSUPPORTED, "tensor-core kernels need f16/bf16 and D in {64, 128}");
+  return ATTN_OK;
+}
+
+attn::Geometry make_geometry(const attn_shape_t* s) {
+  attn::Geometry g;
+  g.BH = s->B * s->H;
+  g.N_q = s->N_q;
+  g.N_kv = s->N_kv;
+  g.D = s->D;
+  g.qi_base = s->chunk_id * s->N_q;
+  g.ki_base = s->chunk_id * s->N_q + s->N_q - s->N_kv;
+  g.window = s->window_size > (1 << 30) ? (1 << 30) : s->window_size;
+  g.mask_mode = s->mask_mode;
+  g.scale = 1.0f / sqrtf((float)s->D);
+  g.scale_log2e = g.scale * attn::kLog2e;
+  return g;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream) {
+  const attn::Geometry g = make_geometry(s);
+  tl_launches = 0;
+  if (g.BH == 0 || (g.N_q == 0 && g.N_kv == 0)) return ATTN_OK;
+  int rc = status_pointer(&t.status);
+  if (rc != ATTN_OK) return rc;
+  const bool use_tc = s->impl == ATTN_IMPL_TENSOR ||
+                      (s->impl == ATTN_IMPL_AUTO && attn::tc_supported(s->dtype, s->D));
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (use_tc) {
+    const char* why = nullptr;
+    e = attn::launch_tc(op, s->dtype, g, t, cs, &tl_launches, &why);
+    if (e != cudaSuccess)
+      return fail(ATTN_ECUDA, "tensor-core launch failed: %s%s%s", cudaGetErrorString(e), why ? ": " : "", why ? why : "");
+  } else {
+    e = attn::launch_simt(op, s->dtype, g, t, cs, &tl_launches);
+    if (e != cudaSuccess) return fail(ATTN_ECUDA, "SIMT launch failed: %s", cudaGetErrorString(e));
+  }
+  tl_error[0] = 0;
+  return ATTN_OK;
+}
+
+#define REQUIRE_PTR(p)                                                       \
+  do {                                                                       \
+    if ((p) == nullptr) return fail(ATTN_EINVAL, #p " is null");             \
+    if (!aligned16(p)) return fail(ATTN_EINVAL, #p " is not 16-byte aligned"); \
+  } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int attn_b200_forward(const attn_shape_t* shape, const void* Q, const void* K, const void* V, void* O,
+                      float* L, void* stream) {
+  int rc = check_shape(shape);
+  if (rc != ATTN_OK) return rc;
+  REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
+  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
+  attn::Tensors t;
+  memset(&t, 0, sizeof(t));
+  t.Q = Q; t.K = K; t.V = V; t.out_O = O; t.out_L = L;
+  return run(attn::OP_FORWARD, shape, t, stream);
+}
+
+size_t attn_b200_backward_scratch_bytes(const attn_shape_t* s) {
+  if (s == nullptr || s->B < 0 || s->H < 0 || s->N_q < 0) return 0;
+  return sizeof(float) * (size_t)s->B * s->H * s->N_q;
+}
+
+int attn_b200_backward(const attn_shape_t* shape, const void* dO, const void* Q, const void* K, const void* V,
+                       const void* O, const float* L, void* dQ, void* dK, void* dV, float* scratch,
+                       void* stream) {
+  int rc = check_shape(shape);
+  if (rc != ATTN_OK) return rc;
+  REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
+  REQUIRE_PTR(dQ); REQUIRE_PTR(dK); REQUIRE_PTR(dV);
+  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
+  if (scratch == nullptr) return fail(ATTN_EINVAL, "scratch is null");
+  attn::Tensors t;
+  memset(&t, 0, sizeof(t));
+  t.dO = dO; t.Q = Q; t.K = K; t.V = V; t.O = O; t.L = L;
+  t.out_dQ = dQ; t.out_dK = dK; t.out_dV = dV;
+  t.Dv = scratch;
+  return run(attn::OP_BACKWARD, shape, t, stream);
+}
+
+size_t attn_b200_double_backward_scratch_bytes(const attn_shape_t* s) {
+  if (s == nullptr || s->B < 0 || s->H < 0 || s->N_q < 0) return 0;
+  return 3 * sizeof(float) * (size_t)s->B * s->H * s->N_q;
+}
+
+int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const void* g_dK, const void* g_dV,
+                              const void* dO, const void* Q, const void* K, const void* V, const void* O,
+                              const float* L, void* g_dO, void* g_Q, void* g_K, void* g_V, float* scratch,
+                              void* stream) {
+  int rc = check_shape(shape);
+  if (rc != ATTN_OK) return rc;
+  REQUIRE_PTR(g_dQ); REQUIRE_PTR(g_dK); REQUIRE_PTR(g_dV);
+  REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V);
+  REQUIRE_PTR(g_dO); REQUIRE_PTR(g_Q); REQUIRE_PTR(g_K); REQUIRE_PTR(g_V);
+  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
+  if (scratch == nullptr) return fail(ATTN_EINVAL, "scratch is null");
+  attn::Tensors t;
+  memset(&t, 0, sizeof(t));
+  t.g_dQ = g_dQ; t.g_dK = g_dK; t.g_dV = g_dV;
+  t.dO = dO; t.Q = Q; t.K = K; t.V = V; t.O = O; t.L = L;
+  t.out_g_dO = g_dO; t.out_g_Q = g_Q; t.out_g_K = g_K; t.out_g_V = g_V;
+  const size_t rows = (size_t)shape->B * shape->H * shape->N_q;
+  t.Dv = scratch;
+  t.dot2 = scratch + rows;
+  t.dot3 = scratch + 2 * rows;
+  return run(attn::OP_DOUBLE_BACKWARD, shape, t, stream);
+}
+
+int attn_b200_last_launch_count(void) { return tl_launches; }
+
+int attn_b200_device_status(uint32_t* code) {
+  unsigned int* p = nullptr;
+  int rc = status_pointer(&p);
+  if (rc != ATTN_OK) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+  unsigned int v = 0;
+  e = cudaMemcpy(&v, p, sizeof(v), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaMemcpy: %s", cudaGetErrorString(e));
+  if (v != 0u) {
+    const unsigned int zero = 0u;
+    cudaMemcpy(p, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+  }
+  if (code != nullptr) *code = v;
+  if (v != 0u) return fail(ATTN_EDEVICE, "kernel gave up on a bounded wait (status 0x%x)", v);
+  return ATTN_OK;
+}
+
+const char* attn_b200_last_error(void) { return tl_error; }
+
+const char* attn_b200_version(void) { return "attn_b200 0.1 (sm_100a)"; }
+
+int attn_b200_selftest_gemm(const void* A, const void* B, float* C, int32_t N, int32_t K, int32_t dtype,
+                            int32_t flags, void* stream) {
+  if (A == nullptr || B == nullptr || C == nullptr) return fail(ATTN_EINVAL, "null pointer");
+  if (!aligned16(A) || !aligned16(B)) return fail(ATTN_EINVAL, "operands must be 16-byte aligned");
+  if ((N != 64 && N != 128) || (K != 64 && K != 128)) return fail(ATTN_EINVAL, "N and K must be 64 or 128");
+  if (dtype != ATTN_F16 && dtype != ATTN_BF16) return fail(ATTN_EUNSUPPORTED, "dtype must be f16 or bf16");
+  unsigned int* status = nullptr;
+  int rc = status_pointer(&status);
+  if (rc != ATTN_OK) return rc;
+  const char* why = nullptr;
+  cudaError_t e = attn::launch_tc_selftest(A, B, C, N, K, dtype, flags, status,
+                                           static_cast<cudaStream_t>(stream), &why);
+  if (e != cudaSuccess)
+    return fail(ATTN_ECUDA, "selftest launch failed: %s%s%s", cudaGetErrorString(e), why ? ": " : "", why ? why : "");
+  tl_launches = 1;
+  return ATTN_OK;
+}
+
+}  // extern "C"

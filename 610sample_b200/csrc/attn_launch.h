@@ -1,0 +1,24 @@
+// Internal launcher interface between the C ABI (attn_capi.cu) and the two
+// kernel families (attn_simt.cu, attn_tc.cu).
+#pragma once
+#include "attn_common.cuh"
+
+namespace attn {
+
+enum Op { OP_FORWARD = 0, OP_BACKWARD = 1, OP_DOUBLE_BACKWARD = 2 };
+
+// fp32 CUDA-core kernels: any dtype, D a multiple of 16 up to 128.
+cudaError_t launch_simt(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,
+                        int* launches);
+
+// tcgen05 tensor-core kernels: f16/bf16, D in {64, 128}.
+bool tc_supported(int dtype, int D);
+cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,
+                      int* launches, const char** err);
+
+// Primitive self-test (one TMA + tcgen05.mma chain), see attn_b200_selftest_gemm.
+cudaError_t launch_tc_selftest(const void* A, const void* B, float* C, int N, int K, int dtype,
+                               int b_layout, unsigned int* status, cudaStream_t s,
+                               const char** err);
+
+}  // namespace attn

@@ -1,0 +1,126 @@
+/*
+ * attn_b200.h -- C ABI of the B200 (sm_100a) attention forward / backward /
+ * double-backward (Hessian-vector product) library, libattn_b200.so.
+ *
+ * Every entry point takes plain device pointers and sizes; no framework types
+ * cross this boundary.  All tensors are dense row-major:
+ *     Q, dO, O, dQ, g_dQ, g_Q, g_dO : [B, H, N_q , D]
+ *     K, V, dK, dV, g_dK, g_dV, g_K, g_V : [B, H, N_kv, D]
+ *     L : [B, H, N_q] float32, natural-log log-sum-exp of the scaled scores
+ * Element type is selected by `dtype` (ATTN_F16 / ATTN_BF16 / ATTN_F32); L and
+ * every scratch buffer are always float32.  The softmax scale is 1/sqrt(D).
+ *
+ * Visibility of key j for query i (mask_mode == ATTN_MASK_REFERENCE):
+ *     qi = chunk_id*N_q + i,  ki = chunk_id*N_q + N_q - N_kv + j
+ *     visible  <=>  ki >= 0  &&  qi >= ki  &&  qi < ki + window_size
+ * which is the predicate of the reference kernels
+ * (csrc/flash_double_backward_v7.cu:100-102 with the index bases of :356, :377).
+ * mask_mode == ATTN_MASK_NONE makes every pair visible (an extension; the
+ * reference cannot express it).  Rows with no visible key give O = 0,
+ * L = -inf and zero gradients.
+ *
+ * Launches are asynchronous on `stream` (a cudaStream_t passed as void*;
+ * NULL = the legacy default stream) of the CURRENT device; inputs are never
+ * written.  Return value: ATTN_OK or a negative ATTN_E* code;
+ * attn_b200_last_error() gives a message for the calling thread.
+ *
+ * These three functions are what the reference's pybind shim binds
+ * (csrc/attention_ext.cpp:4-17: v7_forward_cuda, v7_backward_cuda,
+ * v7_double_backward_cuda) with the tensors flattened to pointers + sizes and
+ * the outputs / scratch allocated by the caller instead of by ATen
+ * (csrc/flash_double_backward_v7.cu:600-601, 1078-1081, 1770-1776).
+ */
+#ifndef ATTN_B200_H
+#define ATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { ATTN_F16 = 0, ATTN_BF16 = 1, ATTN_F32 = 2 };
+enum { ATTN_MASK_REFERENCE = 0, ATTN_MASK_NONE = 1 };
+enum {
+  ATTN_OK = 0,
+  ATTN_EINVAL = -1,      /* bad size / dtype / null pointer / misaligned pointer */
+  ATTN_EUNSUPPORTED = -2, /* head dimension or dtype without a kernel */
+  ATTN_ECUDA = -3,       /* a CUDA runtime/driver call failed */
+  ATTN_EDEVICE = -4,     /* a kernel reported a bounded-wait timeout (see attn_b200_device_status) */
+  ATTN_ETOOLARGE = -5    /* problem exceeds a fixed capacity (static-scratch entry point) */
+};
+
+/* Which kernel family serves a call.  AUTO picks the tcgen05 tensor-core
+ * kernels for f16/bf16 with D in {64, 128} and the fp32 SIMT kernels otherwise
+ * (f32 inputs, D in {16, 32, 48, 80, 96, 112}). */
+enum { ATTN_IMPL_AUTO = 0, ATTN_IMPL_SIMT = 1, ATTN_IMPL_TENSOR = 2 };
+
+typedef struct attn_shape {
+  int32_t B, H, N_q, N_kv, D;
+  int32_t window_size, chunk_id;
+  int32_t mask_mode;  /* ATTN_MASK_* */
+  int32_t dtype;      /* ATTN_F16 / ATTN_BF16 / ATTN_F32 */
+  int32_t impl;       /* ATTN_IMPL_* */
+} attn_shape_t;
+
+/* Forward: O = softmax(mask(Q K^T / sqrt(D))) V and L.
+ * Replaces v7_forward_cuda (reference csrc/flash_double_backward_v7.cu:619-644,
+ * kernel :307-552).  No scratch. */
+int attn_b200_forward(const attn_shape_t* shape, const void* Q, const void* K, const void* V,
+                      void* O, float* L, void* stream);
+
+/* Bytes of float32 scratch attn_b200_backward needs (B*H*N_q floats: the row
+ * term D_i = sum_d dO*O, reference scratch `D_vec`, :1078). */
+size_t attn_b200_backward_scratch_bytes(const attn_shape_t* shape);
+
+/* First backward: dQ, dK, dV from dO and the saved (Q, K, V, O, L).
+ * Replaces v7_backward_cuda (reference :1113-1138, kernels :649-1016). */
+int attn_b200_backward(const attn_shape_t* shape, const void* dO, const void* Q, const void* K,
+                       const void* V, const void* O, const float* L, void* dQ, void* dK, void* dV,
+                       float* scratch, void* stream);
+
+/* Bytes of float32 scratch attn_b200_double_backward needs (3*B*H*N_q floats:
+ * D_i, dot2, dot3 per query row; reference scratch :1770-1772). */
+size_t attn_b200_double_backward_scratch_bytes(const attn_shape_t* shape);
+
+/* Double backward (Hessian-vector product).  Given tangents g_dQ, g_dK, g_dV
+ * on the first backward's outputs, returns the gradients with respect to dO, Q,
+ * K and V (O and L are treated as functions of Q, K, V).  The N_q x N_kv score
+ * matrix is never materialised.  `O` is accepted for signature parity and may
+ * be NULL: D_i is recomputed as sum_j P*dP in float32.
+ * Replaces v7_double_backward_cuda (reference :1815-1842, kernels :1145-1702);
+ * output order as :1809. */
+int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const void* g_dK,
+                              const void* g_dV, const void* dO, const void* Q, const void* K,
+                              const void* V, const void* O, const float* L, void* g_dO, void* g_Q,
+                              void* g_K, void* g_V, float* scratch, void* stream);
+
+/* Number of kernels the last successful call of the calling thread launched. */
+int attn_b200_last_launch_count(void);
+
+/* Reads (and clears) the current device's kernel status word: 0 when no kernel
+ * has given up on a bounded wait since the last read, otherwise a code naming
+ * the kernel and the wait.  Synchronises the device.  Kernels never spin
+ * forever: each wait has an iteration limit, after which the kernel records its
+ * code here and returns. */
+int attn_b200_device_status(uint32_t* code);
+
+/* Message for the last error of the calling thread ("" if none). */
+const char* attn_b200_last_error(void);
+
+/* Library version string. */
+const char* attn_b200_version(void);
+
+/* Tensor-core primitive self-test used by the GPU tests: C[M=128, N] (float32,
+ * row-major) = A[128, K] * Bop, with f16/bf16 operands staged by TMA and
+ * multiplied by one tcgen05.mma chain.  b_layout 0: B given as [N, K]
+ * (K contiguous); 1: B given as [K, N] (N contiguous).  N in {64, 128},
+ * K in {64, 128}.  Has no counterpart in the reference. */
+int attn_b200_selftest_gemm(const void* A, const void* B, float* C, int32_t N, int32_t K,
+                            int32_t dtype, int32_t b_layout, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATTN_B200_H */
