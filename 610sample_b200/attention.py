@@ -31,6 +31,7 @@ class FlashAttentionV7Backward(torch.autograd.Function):
     @staticmethod
     def forward(ctx, dO, Q, K, V, O, L, window_size, chunk_id, mask_mode=0):
         dQ, dK, dV = _attention_cuda.v7_backward(dO, Q, K, V, O, L, window_size, chunk_id, mask_mode)
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(dO, Q, K, V, O, L)
         ctx.window_size = window_size
         ctx.chunk_id = chunk_id
@@ -39,6 +40,8 @@ class FlashAttentionV7Backward(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g_dQ, g_dK, g_dV):
+        if g_dQ is None and g_dK is None and g_dV is None:
+            return (None,) * 9
         dO, Q, K, V, O, L = ctx.saved_tensors
         if g_dQ is None:
             g_dQ = torch.zeros_like(Q)
@@ -56,6 +59,11 @@ class FlashAttentionV7(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, window_size, chunk_id, mask_mode=0):
         O, L = _attention_cuda.v7_forward(Q, K, V, window_size, chunk_id, mask_mode)
+        # The saved O is an input of the differentiable backward below, whose own backward
+        # returns no gradient for it.  Without this flag the engine would turn that missing
+        # gradient into zeros and run a whole first-order backward on them during the
+        # second-order pass.
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(Q, K, V, O, L)
         ctx.window_size = window_size
         ctx.chunk_id = chunk_id
@@ -64,6 +72,8 @@ class FlashAttentionV7(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
+        if grad_output is None:
+            return (None,) * 6
         Q, K, V, O, L = ctx.saved_tensors
         return (*FlashAttentionV7Backward.apply(
             grad_output, Q, K, V, O, L, ctx.window_size, ctx.chunk_id, ctx.mask_mode

@@ -20,6 +20,7 @@ ATTN_OK = 0
 EXPORTS = (
     "attn_b200_forward", "attn_b200_backward_scratch_bytes", "attn_b200_backward",
     "attn_b200_double_backward_scratch_bytes", "attn_b200_double_backward",
+    "attn_b200_double_backward_phases",
     "attn_b200_last_launch_count", "attn_b200_device_status", "attn_b200_last_error",
     "attn_b200_version", "attn_b200_selftest_gemm",
 )
@@ -47,6 +48,7 @@ def lib() -> C.CDLL:
         L.attn_b200_double_backward_scratch_bytes.argtypes = [C.POINTER(Shape)]
         L.attn_b200_double_backward_scratch_bytes.restype = C.c_size_t
         L.attn_b200_double_backward.argtypes = [C.POINTER(Shape)] + [vp] * 13 + [fp, vp]
+        L.attn_b200_double_backward_phases.argtypes = [C.POINTER(Shape)] + [vp] * 13 + [fp, vp, C.c_int32]
         L.attn_b200_device_status.argtypes = [C.POINTER(C.c_uint32)]
         L.attn_b200_last_error.restype = C.c_char_p
         L.attn_b200_version.restype = C.c_char_p

@@ -74,6 +74,7 @@ attn::Geometry make_geometry(const attn_shape_t* s) {
   g.ki_base = s->chunk_id * s->N_q + s->N_q - s->N_kv;
   g.window = s->window_size > (1 << 30) ? (1 << 30) : s->window_size;
   g.mask_mode = s->mask_mode;
+  g.tile_major = 0;
   g.scale = 1.0f / sqrtf((float)s->D);
   g.scale_log2e = g.scale * attn::kLog2e;
   return g;
@@ -81,10 +82,15 @@ attn::Geometry make_geometry(const attn_shape_t* s) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream) {
+int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream, int phases = attn::HVP_PHASE_ALL) {
   const attn::Geometry g = make_geometry(s);
   tl_launches = 0;
   if (g.BH == 0 || (g.N_q == 0 && g.N_kv == 0)) return ATTN_OK;
+  // Bind the device's primary context to this host thread.  Tensor-map encoding is a
+  // driver call and fails with "invalid context" on a thread that has made no runtime
+  // call yet (e.g. a freshly started autograd worker thread).
+  cudaError_t e0 = cudaFree(nullptr);
+  if (e0 != cudaSuccess) return fail(ATTN_ECUDA, "cudaFree(0): %s", cudaGetErrorString(e0));
   int rc = status_pointer(&t.status);
   if (rc != ATTN_OK) return rc;
   const bool use_tc = s->impl == ATTN_IMPL_TENSOR ||
@@ -93,11 +99,11 @@ int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream) {
   cudaError_t e;
   if (use_tc) {
     const char* why = nullptr;
-    e = attn::launch_tc(op, s->dtype, g, t, cs, &tl_launches, &why);
+    e = attn::launch_tc(op, s->dtype, g, t, cs, &tl_launches, &why, phases);
     if (e != cudaSuccess)
       return fail(ATTN_ECUDA, "tensor-core launch failed: %s%s%s", cudaGetErrorString(e), why ? ": " : "", why ? why : "");
   } else {
-    e = attn::launch_simt(op, s->dtype, g, t, cs, &tl_launches);
+    e = attn::launch_simt(op, s->dtype, g, t, cs, &tl_launches, phases);
     if (e != cudaSuccess) return fail(ATTN_ECUDA, "SIMT launch failed: %s", cudaGetErrorString(e));
   }
   tl_error[0] = 0;
@@ -157,6 +163,15 @@ int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const
                               const void* dO, const void* Q, const void* K, const void* V, const void* O,
                               const float* L, void* g_dO, void* g_Q, void* g_K, void* g_V, float* scratch,
                               void* stream) {
+  return attn_b200_double_backward_phases(shape, g_dQ, g_dK, g_dV, dO, Q, K, V, O, L, g_dO, g_Q, g_K, g_V, scratch,
+                                          stream, attn::HVP_PHASE_ALL);
+}
+
+int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ, const void* g_dK,
+                                     const void* g_dV, const void* dO, const void* Q, const void* K, const void* V,
+                                     const void* O, const float* L, void* g_dO, void* g_Q, void* g_K, void* g_V,
+                                     float* scratch, void* stream, int32_t phases) {
+  if (phases <= 0 || phases > attn::HVP_PHASE_ALL) return fail(ATTN_EINVAL, "phases must be a mask in 1..7");
   int rc = check_shape(shape);
   if (rc != ATTN_OK) return rc;
   REQUIRE_PTR(g_dQ); REQUIRE_PTR(g_dK); REQUIRE_PTR(g_dV);
@@ -173,7 +188,7 @@ int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const
   t.Dv = scratch;
   t.dot2 = scratch + rows;
   t.dot3 = scratch + 2 * rows;
-  return run(attn::OP_DOUBLE_BACKWARD, shape, t, stream);
+  return run(attn::OP_DOUBLE_BACKWARD, shape, t, stream, phases);
 }
 
 int attn_b200_last_launch_count(void) { return tl_launches; }
@@ -206,6 +221,8 @@ int attn_b200_selftest_gemm(const void* A, const void* B, float* C, int32_t N, i
   if (!aligned16(A) || !aligned16(B)) return fail(ATTN_EINVAL, "operands must be 16-byte aligned");
   if ((N != 64 && N != 128) || (K != 64 && K != 128)) return fail(ATTN_EINVAL, "N and K must be 64 or 128");
   if (dtype != ATTN_F16 && dtype != ATTN_BF16) return fail(ATTN_EUNSUPPORTED, "dtype must be f16 or bf16");
+  cudaError_t e0 = cudaFree(nullptr);
+  if (e0 != cudaSuccess) return fail(ATTN_ECUDA, "cudaFree(0): %s", cudaGetErrorString(e0));
   unsigned int* status = nullptr;
   int rc = status_pointer(&status);
   if (rc != ATTN_OK) return rc;

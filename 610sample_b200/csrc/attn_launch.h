@@ -7,14 +7,18 @@ namespace attn {
 
 enum Op { OP_FORWARD = 0, OP_BACKWARD = 1, OP_DOUBLE_BACKWARD = 2 };
 
+// Phases of the double backward, as a bit mask (all = 7).  PRE computes the
+// per-row scalars into scratch, ROW the query-side outputs, COL the key-side ones.
+enum HvpPhase { HVP_PHASE_PRE = 1, HVP_PHASE_ROW = 2, HVP_PHASE_COL = 4, HVP_PHASE_ALL = 7 };
+
 // fp32 CUDA-core kernels: any dtype, D a multiple of 16 up to 128.
 cudaError_t launch_simt(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,
-                        int* launches);
+                        int* launches, int phases);
 
 // tcgen05 tensor-core kernels: f16/bf16, D in {64, 128}.
 bool tc_supported(int dtype, int D);
 cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,
-                      int* launches, const char** err);
+                      int* launches, const char** err, int phases);
 
 // Primitive self-test (one TMA + tcgen05.mma chain), see attn_b200_selftest_gemm.
 cudaError_t launch_tc_selftest(const void* A, const void* B, float* C, int N, int K, int dtype,

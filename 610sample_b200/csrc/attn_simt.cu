@@ -466,7 +466,7 @@ static cudaError_t launch_one(const Geometry& g, const Tensors& t, cudaStream_t 
 }
 
 template <typename T>
-static cudaError_t dispatch(int op, const Geometry& g, const Tensors& t, cudaStream_t s, int* n) {
+static cudaError_t dispatch(int op, const Geometry& g, const Tensors& t, cudaStream_t s, int* n, int phases) {
   cudaError_t e = cudaSuccess;
   *n = 0;
   if (op == OP_FORWARD) {
@@ -476,9 +476,9 @@ static cudaError_t dispatch(int op, const Geometry& g, const Tensors& t, cudaStr
     if (e == cudaSuccess) e = launch_one<K_BWD_COL, T>(g, t, s);
     *n = 2;
   } else {
-    e = launch_one<K_HVP_ROW, T>(g, t, s);
-    if (e == cudaSuccess) e = launch_one<K_HVP_COL, T>(g, t, s);
-    *n = 2;
+    // the row kernel computes the per-row scalars itself (its first pass)
+    if (phases & (HVP_PHASE_PRE | HVP_PHASE_ROW)) { e = launch_one<K_HVP_ROW, T>(g, t, s); ++*n; }
+    if (e == cudaSuccess && (phases & HVP_PHASE_COL)) { e = launch_one<K_HVP_COL, T>(g, t, s); ++*n; }
   }
   return e;
 }
@@ -486,11 +486,11 @@ static cudaError_t dispatch(int op, const Geometry& g, const Tensors& t, cudaStr
 }  // namespace simt
 
 cudaError_t launch_simt(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,
-                        int* launches) {
+                        int* launches, int phases) {
   switch (dtype) {
-    case 0: return simt::dispatch<__half>(op, g, t, s, launches);
-    case 1: return simt::dispatch<__nv_bfloat16>(op, g, t, s, launches);
-    default: return simt::dispatch<float>(op, g, t, s, launches);
+    case 0: return simt::dispatch<__half>(op, g, t, s, launches, phases);
+    case 1: return simt::dispatch<__nv_bfloat16>(op, g, t, s, launches, phases);
+    default: return simt::dispatch<float>(op, g, t, s, launches, phases);
   }
 }
 

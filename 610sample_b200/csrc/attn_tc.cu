@@ -33,6 +33,7 @@
 #include "attn_launch.h"
 #include "tc_primitives.cuh"
 
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 
@@ -223,8 +224,8 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_stat = TR::kCol ? g.N_kv : g.N_q;
   const int tiles = (n_stat + BM - 1) / BM;
-  const int bh = blockIdx.x / tiles;
-  const int rank = blockIdx.x - bh * tiles;
+  const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
+  const int rank = g.tile_major ? (int)(blockIdx.x / g.BH) : (int)(blockIdx.x - bh * tiles);
   // heavy tiles first within a head: late query tiles / early key tiles see the most work
   const int tile = (TR::kCol || g.mask_mode != 0) ? rank : (tiles - 1 - rank);
   const int r0 = tile * BM;
@@ -828,10 +829,15 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // [planes][rows][cols] half-precision tensor, box = 64 cols x 64 rows x 1 plane, 128-byte swizzle.
+static thread_local char tl_encode_error[160] = "";
+
 static bool encode_map(CUtensorMap* map, const void* ptr, int is_bf16, long long planes, long long rows,
                        long long cols) {
   EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return false;
+  if (!fn) {
+    snprintf(tl_encode_error, sizeof(tl_encode_error), "driver entry point cuTensorMapEncodeTiled not found");
+    return false;
+  }
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
   cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * (cuuint64_t)cols * 2};
   cuuint32_t box[3] = {64, 64, 1};
@@ -840,16 +846,23 @@ static bool encode_map(CUtensorMap* map, const void* ptr, int is_bf16, long long
                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    snprintf(tl_encode_error, sizeof(tl_encode_error),
+             "cuTensorMapEncodeTiled returned %d for ptr=%p dims=[%lld,%lld,%lld]", (int)r, ptr, planes, rows, cols);
   return r == CUDA_SUCCESS;
 }
 
 template <int KIND, int D, typename T>
-static cudaError_t launch_kind(const TmaMaps& maps, const Geometry& g, const Tensors& t, cudaStream_t s) {
+static cudaError_t launch_kind(const TmaMaps& maps, const Geometry& g_in, const Tensors& t, cudaStream_t s) {
   using TR = Traits<KIND, D>;
+  Geometry g = g_in;
   const int n_stat = TR::kCol ? g.N_kv : g.N_q;
   const long long ctas = (long long)g.BH * ((n_stat + BM - 1) / BM);
   if (ctas <= 0) return cudaSuccess;
   if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  // Few waves: order CTAs heaviest-tile-first across all heads so the tail is made of light
+  // tiles.  Many waves: keep the CTAs of one head adjacent so its K/V tiles stay in L2.
+  g.tile_major = ctas < 8 * 148 ? 1 : 0;
   // at least 120 KB of shared memory per CTA keeps one CTA per SM, so the
   // 512-column tensor-memory allocation can never wait for a co-resident CTA
   const size_t smem = TR::kSmemBytes < 122880u ? 122880u : TR::kSmemBytes;
@@ -862,7 +875,7 @@ static cudaError_t launch_kind(const TmaMaps& maps, const Geometry& g, const Ten
 
 template <int D, typename T>
 static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, const Tensors& t, cudaStream_t s,
-                             int* n) {
+                             int* n, int phases) {
   cudaError_t e = cudaSuccess;
   *n = 0;
   if (op == OP_FORWARD) {
@@ -881,10 +894,9 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
     if (e == cudaSuccess) e = launch_kind<BWD_COL, D, T>(maps, g, t, s);
     *n = 3;
   } else {
-    e = launch_kind<HVP_PRE, D, T>(maps, g, t, s);
-    if (e == cudaSuccess) e = launch_kind<HVP_ROW, D, T>(maps, g, t, s);
-    if (e == cudaSuccess) e = launch_kind<HVP_COL, D, T>(maps, g, t, s);
-    *n = 3;
+    if (phases & HVP_PHASE_PRE) { e = launch_kind<HVP_PRE, D, T>(maps, g, t, s); ++*n; }
+    if (e == cudaSuccess && (phases & HVP_PHASE_ROW)) { e = launch_kind<HVP_ROW, D, T>(maps, g, t, s); ++*n; }
+    if (e == cudaSuccess && (phases & HVP_PHASE_COL)) { e = launch_kind<HVP_COL, D, T>(maps, g, t, s); ++*n; }
   }
   return e;
 }
@@ -894,7 +906,7 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
 bool tc_supported(int dtype, int D) { return (dtype == 0 || dtype == 1) && (D == 64 || D == 128); }
 
 cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s, int* launches,
-                      const char** err) {
+                      const char** err, int phases) {
   using namespace tc;
   *err = nullptr;
   TmaMaps maps;
@@ -906,16 +918,16 @@ cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cu
     const void* p = ptrs[i] ? ptrs[i] : t.Q;   // unused maps still need a valid encoding
     const int r = ptrs[i] ? rows[i] : g.N_q;
     if (!encode_map(&maps.m[i], p, bf, g.BH, r, g.D)) {
-      *err = "cuTensorMapEncodeTiled failed (pointer not 16-byte aligned, or driver entry point missing)";
+      *err = tl_encode_error;
       return cudaErrorInvalidValue;
     }
   }
   if (g.D == 64) {
-    return bf ? launch_op<64, __nv_bfloat16>(op, maps, g, t, s, launches)
-              : launch_op<64, __half>(op, maps, g, t, s, launches);
+    return bf ? launch_op<64, __nv_bfloat16>(op, maps, g, t, s, launches, phases)
+              : launch_op<64, __half>(op, maps, g, t, s, launches, phases);
   }
-  return bf ? launch_op<128, __nv_bfloat16>(op, maps, g, t, s, launches)
-            : launch_op<128, __half>(op, maps, g, t, s, launches);
+  return bf ? launch_op<128, __nv_bfloat16>(op, maps, g, t, s, launches, phases)
+            : launch_op<128, __half>(op, maps, g, t, s, launches, phases);
 }
 
 cudaError_t launch_tc_selftest(const void* A, const void* B, float* C, int N, int K, int dtype, int flags,
@@ -928,7 +940,7 @@ cudaError_t launch_tc_selftest(const void* A, const void* B, float* C, int N, in
   const bool b_mn = (flags & 1) != 0;
   if (!encode_map(&maps.a, A, bf, 1, 128, K) ||
       !encode_map(&maps.b, B, bf, 1, b_mn ? K : N, b_mn ? N : K)) {
-    *err = "cuTensorMapEncodeTiled failed";
+    *err = tl_encode_error;
     return cudaErrorInvalidValue;
   }
   const size_t smem = 4 * 16384 + 1024 + 1024;

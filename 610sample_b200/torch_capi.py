@@ -57,6 +57,17 @@ def double_backward(g_dQ, g_dK, g_dV, dO, Q, K, V, O, L, window_size, chunk_id, 
     return g_dO, g_Q, g_K, g_V
 
 
+def double_backward_phases(g_dQ, g_dK, g_dV, dO, Q, K, V, O, L, window_size, chunk_id, mask_mode=0, impl=0,
+                           scratch=None, out=None, phases=7):
+    """One or more kernels of the double backward (bit mask: 1 scalars, 2 row side, 4 column side)."""
+    s = _shape(Q, K, window_size, chunk_id, mask_mode, impl)
+    g_dO, g_Q, g_K, g_V = out
+    capi.check(capi.lib().attn_b200_double_backward_phases(
+        s, _p(g_dQ), _p(g_dK), _p(g_dV), _p(dO), _p(Q), _p(K), _p(V), _p(O), _p(L),
+        _p(g_dO), _p(g_Q), _p(g_K), _p(g_V), _p(scratch), _stream(), phases), "attn_b200_double_backward_phases")
+    return out
+
+
 def selftest_gemm(A, B, N, K, flags):
     Cout = torch.zeros(128, N, dtype=torch.float32, device=A.device)
     capi.check(capi.lib().attn_b200_selftest_gemm(_p(A), _p(B), _p(Cout), N, K, _DT[A.dtype], flags, _stream()),

@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the double-backward (Hessian-vector product) attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[2], the configuration the metric is quoted on):
+bf16 causal attention double backward, B=4, H=16, N=4096, D=128, all inputs
+N(0,1) from the seeded generator shared with the tests.  One "step" is one
+``v7_double_backward`` call over the whole batch (three kernel launches).
+
+Multi-GPU (``torchrun``, one rank per GPU): the 64 (batch, head) slices are
+partitioned over the ranks with no collective on the kernel path (strong
+scaling: total work fixed); NCCL is used only for the start barrier and the
+max-over-ranks of the measured times.
+
+Printed JSON line: metric = algorithmic TFLOP/s of the HVP
+(2 * D * 12 * visible_pairs * B * H flop per step, recompute not counted).
+``value`` is measured with the inputs resident in HBM; ``e2e`` through the
+``attention_cuda.v7_double_backward`` plugin call with pinned host buffers copied
+in and the four results copied back inside the timed region.
+
+``--impl reference`` times the reference's CPU path (its PyTorch math attention
+differentiated twice; restated in oracle/attention_oracle.py because the
+reference checkout is not present on the GPU box) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(name="hvp_bf16_causal_B4_H16_N4096_D128", B=4, H=16, N=4096, D=128,
+                window_size=4096, chunk_id=0, mask_mode=0)
+HVP_GEMMS = 12          # algorithmic contractions of the double backward
+ROW_KERNEL_GEMMS = 9    # contractions the row kernel executes (5 score + 4 output)
+PRE_KERNEL_GEMMS = 5
+COL_KERNEL_GEMMS = 8
+
+
+def visible_pairs_causal(n: int) -> int:
+    return n * (n + 1) // 2
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16_tflops=float(p["bf16_tflops"]), bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", 0)),
+                    hbm_gbs=float(p["hbm_gbs"]), source="measured")
+    return dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(smax) if smax else None,
+                    samples=len(sm), reasons=sorted(reasons))
+
+
+def cpu_hvp_seconds(orc, torch, n_heads: int, N: int, D: int, seed: int = 0):
+    """Time the reference CPU path (math attention, double autograd) on `n_heads`
+    (batch, head) slices of the workload; returns (seconds for the HVP step, threads)."""
+    inp = orc.make_inputs(1, n_heads, N, N, D, seed=seed, dtype=torch.float32)
+    mask = orc.visibility_mask(0, N, N, N)
+    total = 0.0
+    for h in range(n_heads):
+        q, k, v, do = (inp[n][:, h:h + 1].clone().requires_grad_(True) for n in ("Q", "K", "V", "dO"))
+        O = orc.math_attention(q, k, v, mask)
+        dQ, dK, dV = torch.autograd.grad(O, [q, k, v], grad_outputs=do, create_graph=True)
+        hsum = (dQ * inp["g_dQ"][:, h:h + 1]).sum() + (dK * inp["g_dK"][:, h:h + 1]).sum() + (dV * inp["g_dV"][:, h:h + 1]).sum()
+        t0 = time.perf_counter()
+        torch.autograd.grad(hsum, [do, q, k, v])
+        total += time.perf_counter() - t0
+    return total, torch.get_num_threads()
+
+
+def run_reference(args):
+    """CPU arm: the reference's own CPU implementation of the path on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import attention_oracle as orc
+    w = WORKLOAD
+    torch.set_num_threads(os.cpu_count() or 1)
+    heads_per_step = 4
+    flops_head = 2.0 * w["D"] * HVP_GEMMS * visible_pairs_causal(w["N"])
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_hvp_seconds(orc, torch, 1, w["N"], w["D"])
+    times = []
+    for s in range(args.steps):
+        sec, threads = cpu_hvp_seconds(orc, torch, heads_per_step, w["N"], w["D"], seed=s)
+        times.append(sec)
+    sec = sum(times) / len(times)
+    value = flops_head * heads_per_step / sec / 1e12
+    sample = f"{heads_per_step} of {w['B'] * w['H']} (batch, head) slices per step, fp32, second autograd.grad only"
+    line = {
+        "impl": "reference", "metric": "hvp_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import attention_oracle as orc
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg_dir = os.path.join(ROOT, "610sample_b200")
+    sys.path.insert(0, pkg_dir)
+    import attention_cuda                                   # the plugin module (fails loudly if not built)
+    tcapi = importlib.import_module("610sample_b200.torch_capi")
+    capi = importlib.import_module("610sample_b200.capi")
+
+    w = WORKLOAD
+    BH = w["B"] * w["H"]
+    assert BH % world == 0, "batch*heads must divide over the ranks"
+    bh_local = BH // world
+    N, D = w["N"], w["D"]
+    # every rank draws the full seeded workload and keeps its contiguous slice of (batch, head)
+    full = orc.make_inputs(1, BH, N, N, D, seed=0, dtype=torch.bfloat16)
+    sl = slice(rank * bh_local, (rank + 1) * bh_local)
+    host = {n: full[n][:, sl].contiguous().pin_memory() for n in orc.INPUT_NAMES}
+    del full
+    g = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
+    ws, cid, mm = w["window_size"], w["chunk_id"], w["mask_mode"]
+
+    O, L = tcapi.forward(g["Q"], g["K"], g["V"], ws, cid, mm)
+    host_O = torch.empty_like(O, device="cpu").pin_memory(); host_O.copy_(O)
+    host_L = torch.empty_like(L, device="cpu").pin_memory(); host_L.copy_(L)
+    s = tcapi._shape(g["Q"], g["K"], ws, cid, mm, 0)
+    scratch = torch.empty(capi.lib().attn_b200_double_backward_scratch_bytes(s) // 4 + 4, dtype=torch.float32, device=dev)
+    outs = tuple(torch.empty_like(g[n]) for n in ("Q", "Q", "K", "V"))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # > 126 MB L2
+
+    def step():
+        tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, ws, cid, mm,
+                              scratch=scratch, out=outs)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    launches_per_step = capi.lib().attn_b200_last_launch_count()
+    torch.cuda.synchronize()
+
+    # ---- kernel-resident timing ------------------------------------------------
+    sampler = ClockSampler(local)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    sampler.start()
+    for a, b in ev:
+        flush.zero_()
+        a.record()
+        step()
+        b.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b) for a, b in ev)
+    tm = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    ms_per_step = float(tm.item()) / args.steps
+
+    # ---- per-kernel timing of the dominant kernel (rank 0, single-GPU roofline) --
+    phase_ms = {}
+    if hasattr(capi.lib(), "attn_b200_double_backward_phases"):
+        for name, mask_bits in (("pre", 1), ("row", 2), ("col", 4)):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            tot = 0.0
+            reps = max(3, min(args.steps, 10))
+            for _ in range(reps):
+                flush.zero_()
+                a.record()
+                tcapi.double_backward_phases(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L,
+                                             ws, cid, mm, scratch=scratch, out=outs, phases=mask_bits)
+                b.record()
+                torch.cuda.synchronize()
+                tot += a.elapsed_time(b)
+            phase_ms[name] = tot / reps
+
+    # ---- end to end through the plugin call, host buffers ------------------------
+    e2e_steps = max(1, min(args.steps, 5))
+    in_names = ("g_dQ", "g_dK", "g_dV", "dO", "Q", "K", "V")
+    host_out = [torch.empty_like(t, device="cpu").pin_memory() for t in outs]
+    h2d = sum(host[n].numel() * host[n].element_size() for n in in_names) + host_O.numel() * 2 + host_L.numel() * 4
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def e2e_step():
+        d = {n: host[n].to(dev, non_blocking=True) for n in in_names}
+        dO_, dL_ = host_O.to(dev, non_blocking=True), host_L.to(dev, non_blocking=True)
+        r = attention_cuda.v7_double_backward(d["g_dQ"], d["g_dK"], d["g_dV"], d["dO"], d["Q"], d["K"], d["V"], dO_, dL_, ws, cid)
+        for dst, src in zip(host_out, r):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    barrier()
+    te = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / e2e_steps
+    status = capi.device_status()
+
+    flops_step = 2.0 * D * HVP_GEMMS * visible_pairs_causal(N) * BH          # whole job, all ranks
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+    e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+    peaks = read_peaks()
+
+    if rank == 0:
+        line = {
+            "metric": "hvp_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "parallelism": f"batch*head sharded over {world} GPU(s), no collective",
+                       "l2": "256 MB buffer written between timed steps", "heads_per_gpu": bh_local,
+                       "flop_model": "2*D*12*visible_pairs*B*H"},
+            "pct_of_bf16_peak": 100.0 * value / (peaks["bf16_tflops"] * world),
+            "pct_of_bf16_peak_sustained": (100.0 * value / (peaks["bf16_tflops_sustained"] * world)
+                                           if peaks["bf16_tflops_sustained"] else None),
+            "peaks": peaks, "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world},
+            "gpu_launches": int(launches_per_step) * args.steps,
+            "device_status": status,
+        }
+        if phase_ms and world == 1:
+            pairs = visible_pairs_causal(N) * BH
+            k_flops = {"pre": PRE_KERNEL_GEMMS, "row": ROW_KERNEL_GEMMS, "col": COL_KERNEL_GEMMS}
+            dom = max(phase_ms, key=phase_ms.get)
+            ach = 2.0 * D * k_flops[dom] * pairs / (phase_ms[dom] * 1e-3) / 1e12
+            line["roofline"] = {"bound": "tensor", "kernel": "hvp_" + dom, "achieved": ach, "peak": peaks["bf16_tflops"],
+                                "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "traffic": None,
+                                "peak_source": peaks["source"],
+                                "kernel_ms": phase_ms, "gemms_counted": k_flops[dom]}
+        if world == 1 and not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
+            n_cpu = 16
+            sec, threads = cpu_hvp_seconds(orc, torch, n_cpu, N, D)
+            cpu_val = 2.0 * D * HVP_GEMMS * visible_pairs_causal(N) * n_cpu / sec / 1e12
+            line["cpu_baseline"] = {"value": cpu_val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": f"{n_cpu} of {BH} (batch, head) slices, fp32 math attention, "
+                                              f"second autograd.grad only ({sec:.2f} s timed)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

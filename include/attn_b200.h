@@ -48,7 +48,7 @@ enum {
   ATTN_EUNSUPPORTED = -2, /* head dimension or dtype without a kernel */
   ATTN_ECUDA = -3,       /* a CUDA runtime/driver call failed */
   ATTN_EDEVICE = -4,     /* a kernel reported a bounded-wait timeout (see attn_b200_device_status) */
-  ATTN_ETOOLARGE = -5    /* problem exceeds a fixed capacity (static-scratch entry point) */
+  ATTN_ETOOLARGE = -5    /* problem exceeds a fixed capacity */
 };
 
 /* Which kernel family serves a call.  AUTO picks the tcgen05 tensor-core
@@ -96,6 +96,18 @@ int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const
                               const void* V, const void* O, const float* L, void* g_dO, void* g_Q,
                               void* g_K, void* g_V, float* scratch, void* stream);
 
+/* The same computation restricted to some of its kernels, for profiling one
+ * kernel at a time: `phases` is a bit mask of 1 (per-row scalars Dv, dot2, dot3
+ * into scratch), 2 (g_Q and g_dO; needs the scalars in scratch) and 4 (g_K and
+ * g_V; needs the scalars too).  7 is attn_b200_double_backward.  The reference
+ * splits its double backward the same way into kernel A (rows, two passes) and
+ * kernel B (columns), csrc/flash_double_backward_v7.cu:1778-1807. */
+int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ, const void* g_dK,
+                                     const void* g_dV, const void* dO, const void* Q, const void* K,
+                                     const void* V, const void* O, const float* L, void* g_dO,
+                                     void* g_Q, void* g_K, void* g_V, float* scratch, void* stream,
+                                     int32_t phases);
+
 /* Number of kernels the last successful call of the calling thread launched. */
 int attn_b200_last_launch_count(void);
 
@@ -113,12 +125,13 @@ const char* attn_b200_last_error(void);
 const char* attn_b200_version(void);
 
 /* Tensor-core primitive self-test used by the GPU tests: C[M=128, N] (float32,
- * row-major) = A[128, K] * Bop, with f16/bf16 operands staged by TMA and
- * multiplied by one tcgen05.mma chain.  b_layout 0: B given as [N, K]
- * (K contiguous); 1: B given as [K, N] (N contiguous).  N in {64, 128},
- * K in {64, 128}.  Has no counterpart in the reference. */
+ * row-major) = A[128, K] * Bop, with f16/bf16 operands in 128-byte-swizzled
+ * shared memory and one tcgen05.mma chain.  flags bit 0: B is given as [K, N]
+ * (N contiguous, read as an MN-major operand) instead of [N, K]; bit 1: A is
+ * staged by the threads with the software swizzle instead of by TMA.
+ * N in {64, 128}, K in {64, 128}.  Has no counterpart in the reference. */
 int attn_b200_selftest_gemm(const void* A, const void* B, float* C, int32_t N, int32_t K,
-                            int32_t dtype, int32_t b_layout, void* stream);
+                            int32_t dtype, int32_t flags, void* stream);
 
 #ifdef __cplusplus
 }

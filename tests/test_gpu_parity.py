@@ -1,0 +1,166 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU
+oracle and the golden fixtures produced by the reference's own code.
+
+Tolerances
+  * fp32 inputs (SIMT kernels): norm-wise relative error < 1e-4 against the fp64 oracle.
+  * bf16 / fp16 inputs: every output within `HALF_RTOL * max|ref| ` max-abs of the fp64
+    oracle evaluated on the same rounded inputs (bf16 2.0e-2, fp16 3e-3: output rounding
+    alone is 2^-9 resp. 2^-12 relative), and, for bf16, max-abs error no worse than 2x that
+    of the reference path (PyTorch math attention differentiated twice in bf16).
+"""
+import importlib
+import math
+
+import pytest
+import torch
+
+import attention_oracle as orc
+from _util import golden_case_names, load_config1_head, load_golden
+
+pytestmark = pytest.mark.gpu
+
+tcapi = importlib.import_module("610sample_b200.torch_capi")
+capi = importlib.import_module("610sample_b200.capi")
+
+HALF_RTOL = {torch.bfloat16: 2.0e-2, torch.float16: 3.0e-3}
+DEV = "cuda"
+
+
+def run_all(inp, ws, cid, mm, impl):
+    g = {n: t.to(DEV) for n, t in inp.items()}
+    O, L = tcapi.forward(g["Q"], g["K"], g["V"], ws, cid, mm, impl)
+    dQ, dK, dV = tcapi.backward(g["dO"], g["Q"], g["K"], g["V"], O, L, ws, cid, mm, impl)
+    g_dO, g_Q, g_K, g_V = tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"],
+                                                O, L, ws, cid, mm, impl)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    out = dict(O=O, L=L, dQ=dQ, dK=dK, dV=dV, g_dO=g_dO, g_Q=g_Q, g_K=g_K, g_V=g_V)
+    return {n: t.float().cpu() for n, t in out.items()}
+
+
+def check_half(got, ref, dtype, what=""):
+    for n in orc.OUTPUT_NAMES:
+        r = torch.nan_to_num(ref[n].double(), neginf=0.0)
+        v = got[n].double()
+        if n == "L":
+            assert torch.equal(torch.isinf(got[n]), torch.isinf(ref[n].float())), f"{what} L: -inf rows differ"
+            v = torch.nan_to_num(v, neginf=0.0)
+            assert (v - r).abs().max() <= 1e-4 * max(1.0, float(r.abs().max())), f"{what} L"
+            continue
+        assert torch.isfinite(v).all(), f"{what} {n}: non-finite values"
+        tol = HALF_RTOL[dtype] * max(1.0, float(r.abs().max()))
+        err = float((v - r).abs().max())
+        assert err <= tol, f"{what} {n}: max-abs {err:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("name", golden_case_names())
+@pytest.mark.parametrize("impl", ["simt", "tensor"])
+def test_golden_fixtures(name, impl):
+    meta, inp, ref, _ = load_golden(name)
+    if impl == "tensor" and meta["D"] not in (64, 128):
+        pytest.skip("tensor-core kernels cover D in {64, 128}")
+    got = run_all(inp, meta["window_size"], meta["chunk_id"], 0, 1 if impl == "simt" else 2)
+    check_half(got, ref, torch.bfloat16, f"{name}/{impl}")
+
+
+def test_fp32_reference_config_within_1e4():
+    """CPU-runnable reference case: causal, fp32, B2 H4 N256 D64, seed 0."""
+    (b, h), _, head_ref, norms, _ = load_config1_head()
+    inp = orc.make_inputs(2, 4, 256, 256, 64, seed=0, dtype=torch.float32)
+    got = run_all(inp, 256, 0, 0, 0)
+    for n in orc.OUTPUT_NAMES:
+        assert orc.rel_err(got[n][b, h], head_ref[n]) < 1e-4, n
+        assert abs(float(got[n].double().norm()) - norms[n]) < 1e-4 * norms[n], n
+    ref = orc.closed_form_all(*(inp[n] for n in orc.INPUT_NAMES), window_size=256, chunk_id=0)
+    for n in orc.OUTPUT_NAMES:
+        assert orc.rel_err(got[n], ref[n]) < 1e-4, n
+
+
+def reference_path_errors(inp, mask, oracle):
+    """max-abs error of the reference path (math attention, double autograd) run in the
+    inputs' own half precision on the GPU, against the fp64 oracle."""
+    dt = inp["Q"].dtype
+    out = orc.autograd_all(*(inp[n].to(DEV) for n in orc.INPUT_NAMES), mask.to(DEV), compute_dtype=dt)
+    return {n: orc.max_abs_err(out[n].float().cpu(), oracle[n]) for n in orc.OUTPUT_NAMES if n != "L"}
+
+
+@pytest.mark.parametrize("shape", [
+    # B, H, N_q, N_kv, D, window, chunk, mask_mode, qk_scale
+    (2, 2, 512, 512, 128, 512, 0, 0, 1.0),       # causal, the headline head dimension
+    (1, 4, 512, 512, 64, 512, 0, 1, 0.5),        # no mask, inputs scaled like the non-causal config
+    (1, 2, 384, 640, 64, 300, 2, 0, 1.0),        # rectangular sliding window
+    (1, 2, 512, 512, 128, 512, 0, 0, 2.0),       # peaked softmax rows
+])
+def test_bf16_error_within_twice_reference_path(shape):
+    B, H, Nq, Nkv, D, ws, cid, mm, qk = shape
+    inp = orc.make_inputs(B, H, Nq, Nkv, D, seed=1, dtype=torch.bfloat16, qk_scale=qk, v_scale=0.5 if mm else 1.0)
+    oracle = orc.closed_form_all(*(inp[n] for n in orc.INPUT_NAMES), window_size=ws, chunk_id=cid, mask_mode=mm)
+    got = run_all(inp, ws, cid, mm, 2)
+    ref_err = reference_path_errors(inp, orc.visibility_mask(cid, Nq, Nkv, ws, mm), oracle)
+    for n, e_ref in ref_err.items():
+        e = orc.max_abs_err(got[n], oracle[n])
+        assert e <= 2.0 * e_ref + 1e-6, f"{n}: ours {e:.3e} vs reference path {e_ref:.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [
+    (1, 1, 1, 1, 64, 1, 0, 0), (1, 1, 129, 65, 64, 1000, 0, 0), (1, 2, 200, 333, 128, 77, 3, 0),
+    (1, 1, 64, 512, 128, 512, 0, 0), (2, 1, 300, 300, 64, 300, 0, 1), (1, 1, 96, 40, 128, 1000, 0, 0),
+    (1, 3, 640, 640, 128, 1, 0, 0),
+])
+def test_ragged_and_edge_shapes_tensor(shape, dtype):
+    B, H, Nq, Nkv, D, ws, cid, mm = shape
+    inp = orc.make_inputs(B, H, Nq, Nkv, D, seed=2, dtype=dtype)
+    oracle = orc.closed_form_all(*(inp[n] for n in orc.INPUT_NAMES), window_size=ws, chunk_id=cid, mask_mode=mm)
+    got = run_all(inp, ws, cid, mm, 2)
+    check_half(got, oracle, dtype, str(shape))
+
+
+@pytest.mark.parametrize("D", [16, 48, 80, 96, 112])
+def test_other_head_dims_simt(D):
+    inp = orc.make_inputs(1, 2, 70, 150, D, seed=3, dtype=torch.bfloat16)
+    oracle = orc.closed_form_all(*(inp[n] for n in orc.INPUT_NAMES), window_size=100, chunk_id=1)
+    got = run_all(inp, 100, 1, 0, 0)       # AUTO must pick the SIMT kernels here
+    check_half(got, oracle, torch.bfloat16, f"D={D}")
+
+
+def test_bitwise_reproducible():
+    inp = orc.make_inputs(2, 3, 700, 700, 128, seed=4, dtype=torch.bfloat16)
+    a = run_all(inp, 700, 0, 0, 2)
+    b = run_all(inp, 700, 0, 0, 2)
+    for n in orc.OUTPUT_NAMES:
+        assert torch.equal(a[n], b[n]), n
+
+
+def test_tensor_kernels_agree_with_simt_at_n2048():
+    """Larger than the oracle finishes quickly on a CPU: the fp32 SIMT kernels (pinned
+    against the oracle above) check the tensor-core kernels on the same bf16 inputs."""
+    inp = orc.make_inputs(1, 2, 2048, 2048, 128, seed=5, dtype=torch.bfloat16)
+    a = run_all(inp, 2048, 0, 0, 2)
+    b = run_all(inp, 2048, 0, 0, 1)
+    for n in orc.OUTPUT_NAMES:
+        if n == "L":
+            assert (a[n] - b[n]).abs().max() < 1e-4
+        else:
+            tol = HALF_RTOL[torch.bfloat16] * float(b[n].abs().max())
+            assert float((a[n] - b[n]).abs().max()) <= tol, n
+
+
+def test_linearity_in_tangents_at_headline_size():
+    """Size-independent property at N=4096, D=128 causal: the HVP is linear in the tangents,
+    HVP(a*g) == a*HVP(g) exactly for a power of two, and HVP(0) == 0."""
+    inp = orc.make_inputs(1, 2, 4096, 4096, 128, seed=6, dtype=torch.bfloat16)
+    g = {n: t.to(DEV) for n, t in inp.items()}
+    O, L = tcapi.forward(g["Q"], g["K"], g["V"], 4096, 0)
+    base = tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, 4096, 0)
+    twice = tcapi.double_backward(2 * g["g_dQ"], 2 * g["g_dK"], 2 * g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, 4096, 0)
+    z = torch.zeros_like
+    zero = tcapi.double_backward(z(g["Q"]), z(g["K"]), z(g["V"]), g["dO"], g["Q"], g["K"], g["V"], O, L, 4096, 0)
+    torch.cuda.synchronize()
+    for a, b, c in zip(base, twice, zero):
+        assert torch.equal((2 * a.float()), b.float())
+        assert float(c.float().abs().max()) == 0.0
+    # softmax rows sum to one: with V = 1 the forward output is exactly 1 up to rounding
+    O1, _ = tcapi.forward(g["Q"], g["K"], torch.ones_like(g["V"]), 4096, 0)
+    assert float((O1.float() - 1).abs().max()) < 1e-2
+    assert capi.device_status() == 0
