@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -75,6 +76,10 @@ attn::Geometry make_geometry(const attn_shape_t* s) {
   g.window = s->window_size > (1 << 30) ? (1 << 30) : s->window_size;
   g.mask_mode = s->mask_mode;
   g.tile_major = 0;
+  g.debug = 0;
+#ifdef ATTN_EXPERIMENT
+  if (const char* e = getenv("ATTN_B200_DEBUG")) g.debug = atoi(e);
+#endif
   g.scale = 1.0f / sqrtf((float)s->D);
   g.scale_log2e = g.scale * attn::kLog2e;
   return g;

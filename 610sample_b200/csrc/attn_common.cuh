@@ -30,6 +30,7 @@ struct Geometry {
   int ki_base;   // absolute index of key row 0    (= chunk_id * N_q + N_q - N_kv)
   int window;    // clamped to 2^30 so qi < ki + window never overflows
   int mask_mode; // 0 reference mask, 1 none
+  int debug;       // experiment switches; only read by builds with ATTN_EXPERIMENT defined
   int tile_major;  // CTA order: 0 = head-major (L2 locality), 1 = tile-major (balance on small grids)
   float scale;       // 1/sqrt(D)
   float scale_log2e; // scale * log2(e)

@@ -31,7 +31,7 @@
 // there are no atomics.
 #include "attn_common.cuh"
 #include "attn_launch.h"
-#include "tc_primitives.cuh"
+#include "tc_common.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -39,23 +39,6 @@
 
 namespace attn {
 namespace tc {
-
-constexpr int BM = 128;            // stationary rows per CTA
-constexpr int BN = 64;             // streamed rows per iteration
-constexpr int kMathWarps = 8;
-constexpr int kMathThreads = kMathWarps * 32;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
-constexpr int kTmemCols = 512;
-constexpr uint32_t kAtomBytesStat = BM * 128;   // [128 rows][64 halves], 16 KB
-constexpr uint32_t kAtomBytesStrm = BN * 128;   // [ 64 rows][64 halves],  8 KB
-constexpr uint32_t kOpTileBytes = BM * 128;     // [128 rows][64 halves], 16 KB
-
-enum Kind { FWD_LSE = 0, FWD_OUT, BWD_ROW, BWD_COL, HVP_PRE, HVP_ROW, HVP_COL };
-enum TensorId { T_Q = 0, T_K, T_V, T_dO, T_gQ, T_gK, T_gV, T_COUNT };
-
-struct TmaMaps { CUtensorMap m[T_COUNT]; };
 
 // ---------------------------------------------------------------------------
 // per-kind configuration
@@ -138,59 +121,6 @@ struct Traits {
   }
 };
 
-// Shared-memory control block (lives in the aux area).
-struct Control {
-  uint64_t stat_full;
-  uint64_t stream_full[2];
-  uint64_t stream_empty[2];
-  uint64_t score_full[2];
-  uint64_t score_free[2];
-  uint64_t opnd_full;
-  uint64_t opnd_free;
-  uint64_t acc_done;
-  uint64_t stats_ready[2];
-  uint32_t tmem_base;
-  volatile uint32_t abort_flag;
-};
-
-// status codes: (kind + 1) << 8 | wait id
-__device__ __forceinline__ uint32_t wait_code(int kind, int id) { return ((uint32_t)(kind + 1) << 8) | (uint32_t)id; }
-
-template <typename T> struct Pack;
-template <> struct Pack<__nv_bfloat16> {
-  static constexpr int kIsBf16 = 1;
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-template <> struct Pack<__half> {
-  static constexpr int kIsBf16 = 0;
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// 16 packed halves (two 16-byte chunks) of operand-tile row `row`, columns
-// [col0, col0+16), into a 128-byte-swizzled [128][64] tile.
-__device__ __forceinline__ void store_op16(uint32_t tile, int row, int col0, const uint32_t (&v)[8]) {
-  const uint32_t a0 = tile + sw128_offset(row, col0);
-  const uint32_t a1 = tile + sw128_offset(row, col0 + 8);
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a0), "r"(v[0]), "r"(v[1]), "r"(v[2]),
-               "r"(v[3])
-               : "memory");
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a1), "r"(v[4]), "r"(v[5]), "r"(v[6]),
-               "r"(v[7])
-               : "memory");
-}
-
 // ---------------------------------------------------------------------------
 // the engine
 // ---------------------------------------------------------------------------
@@ -222,6 +152,11 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   float* aux_f = reinterpret_cast<float*>(smem_gen + aux_off + 256);   // 512 floats when present
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ATTN_EXPERIMENT
+  const bool dbg_skip_math = (g.debug & 1) != 0, dbg_skip_mma = (g.debug & 2) != 0;
+#else
+  constexpr bool dbg_skip_math = false, dbg_skip_mma = false;
+#endif
   const int n_stat = TR::kCol ? g.N_kv : g.N_q;
   const int tiles = (n_stat + BM - 1) / BM;
   const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
@@ -387,7 +322,7 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         if (!mbar_wait(bar_opnd_full, k & 1, abort_flag, t.status, wait_code(KIND, 5))) return false;
         tc_fence_after_sync();
         const int st = k % TR::kStages;
-        issue_outs(strm_base + st * TR::kStageBytes, k == 0);
+        if (!dbg_skip_mma) issue_outs(strm_base + st * TR::kStageBytes, k == 0);
         mma_commit(bar_opnd_free);
         mma_commit(bar_stream_empty(st));
         return true;
@@ -400,7 +335,7 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         ok = mbar_wait(bar_score_free(sb), ((it / TR::kScoreBufs) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 4));
         if (!ok) break;
         tc_fence_after_sync();
-        issue_scores(strm_base + st * TR::kStageBytes, sb);
+        if (!dbg_skip_mma) issue_scores(strm_base + st * TR::kStageBytes, sb);
         mma_commit(bar_score_full(sb));
         if constexpr (TR::kReduce) {
           mma_commit(bar_stream_empty(st));
@@ -480,6 +415,11 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       const float* cs = col_stats + (it & 1) * 256;
       (void)cs;
 
+      if (dbg_skip_math) {
+        if constexpr (!TR::kReduce) {
+          if (it > 0) ok = mbar_wait(bar_opnd_free, (it - 1) & 1, abort_flag, t.status, wait_code(KIND, 7));
+        }
+      } else
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const int c0 = half * 32 + ch * 16;    // column inside the 64-wide tile
@@ -725,7 +665,7 @@ selftest_gemm_kernel(const __grid_constant__ SelftestMaps maps, const T* __restr
   const uint32_t b_base = base + 2 * 16384;     // up to 32 KB
   Control* ctl = reinterpret_cast<Control*>(gen + 4 * 16384);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool b_mn = (flags & 1) != 0, a_manual = (flags & 2) != 0;
+  const bool b_mn = (flags & 1) != 0, a_manual = (flags & 2) != 0, a_tmem = (flags & 4) != 0;
   const uint32_t bar_full = smem_u32(&ctl->stat_full), bar_done = smem_u32(&ctl->acc_done);
   if (threadIdx.x == 0) {
     mbar_init(bar_full, 1);
@@ -735,14 +675,27 @@ selftest_gemm_kernel(const __grid_constant__ SelftestMaps maps, const T* __restr
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem_base), 128);
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem_base), 256);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
-  if (a_manual) {
+  if (a_tmem) {
+    // every thread stores its own row of A into tensor memory, two halves per 32-bit column,
+    // starting at column 128
+    const int row = threadIdx.x;
+    for (int w0 = 0; w0 < K / 2; w0 += 8) {
+      uint32_t v[8];
+      const uint4 x0 = *reinterpret_cast<const uint4*>(A_gmem + (size_t)row * K + 2 * w0);
+      const uint4 x1 = *reinterpret_cast<const uint4*>(A_gmem + (size_t)row * K + 2 * w0 + 8);
+      v[0] = x0.x; v[1] = x0.y; v[2] = x0.z; v[3] = x0.w; v[4] = x1.x; v[5] = x1.y; v[6] = x1.z; v[7] = x1.w;
+      tmem_st8(tmem_base + ((uint32_t)(warp * 32) << 16) + 128 + w0, v);
+    }
+    tmem_st_wait();
+    tc_fence_before_sync();
+  } else if (a_manual) {
     // every thread writes its own row of A with the software swizzle
     const int row = threadIdx.x;
     for (int c = 0; c < K; c += 8) {
@@ -757,10 +710,11 @@ selftest_gemm_kernel(const __grid_constant__ SelftestMaps maps, const T* __restr
   const int ka = K / 64;
   if (threadIdx.x == 0) {
     uint32_t bytes = 0;
-    if (!a_manual) bytes += 128 * K * 2;
+    const bool a_tma = !a_manual && !a_tmem;
+    if (a_tma) bytes += 128 * K * 2;
     bytes += N * K * 2;
     mbar_arrive_expect_tx(bar_full, bytes);
-    if (!a_manual)
+    if (a_tma)
       for (int a = 0; a < ka; ++a)
         for (int h = 0; h < 2; ++h) tma_load_3d(a_base + a * 16384 + h * 8192, &maps.a, a * 64, h * 64, 0, bar_full);
     if (!b_mn) {
@@ -782,7 +736,8 @@ selftest_gemm_kernel(const __grid_constant__ SelftestMaps maps, const T* __restr
         uint64_t bd;
         if (!b_mn) bd = smem_desc_sw128(b_base + (ks >> 2) * (N * 128) + (ks & 3) * 32, 16, 1024);
         else bd = smem_desc_sw128(b_base + ks * 2048, K * 128, 1024);
-        mma_ss(tmem_base, ad, bd, idesc, ks > 0);
+        if (a_tmem) mma_ts(tmem_base, tmem_base + 128 + ks * 8, bd, idesc, ks > 0);
+        else mma_ss(tmem_base, ad, bd, idesc, ks > 0);
       }
       mma_commit(bar_done);
     }
@@ -803,7 +758,7 @@ selftest_gemm_kernel(const __grid_constant__ SelftestMaps maps, const T* __restr
   __syncthreads();
   if (warp == 0) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 128);
+    tmem_dealloc(tmem_base, 256);
   }
 }
 
@@ -852,6 +807,24 @@ static bool encode_map(CUtensorMap* map, const void* ptr, int is_bf16, long long
   return r == CUDA_SUCCESS;
 }
 
+bool encode_all_maps(TmaMaps* maps, const Geometry& g, const Tensors& t, int is_bf16, const char** err) {
+  memset(maps, 0, sizeof(*maps));
+  const void* ptrs[T_COUNT] = {t.Q, t.K, t.V, t.dO, t.g_dQ, t.g_dK, t.g_dV};
+  const int rows[T_COUNT] = {g.N_q, g.N_kv, g.N_kv, g.N_q, g.N_q, g.N_kv, g.N_kv};
+  for (int i = 0; i < T_COUNT; ++i) {
+    const void* p = ptrs[i] ? ptrs[i] : t.Q;   // unused maps still need a valid encoding
+    const int r = ptrs[i] ? rows[i] : g.N_q;
+    if (!encode_map(&maps->m[i], p, is_bf16, g.BH, r, g.D)) {
+      *err = tl_encode_error;
+      return false;
+    }
+  }
+  return true;
+}
+
+cudaError_t launch_hvp_main(bool col, int D, int is_bf16, const TmaMaps& maps, const Geometry& g,
+                            const Tensors& t, cudaStream_t s);
+
 template <int KIND, int D, typename T>
 static cudaError_t launch_kind(const TmaMaps& maps, const Geometry& g_in, const Tensors& t, cudaStream_t s) {
   using TR = Traits<KIND, D>;
@@ -895,8 +868,16 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
     *n = 3;
   } else {
     if (phases & HVP_PHASE_PRE) { e = launch_kind<HVP_PRE, D, T>(maps, g, t, s); ++*n; }
-    if (e == cudaSuccess && (phases & HVP_PHASE_ROW)) { e = launch_kind<HVP_ROW, D, T>(maps, g, t, s); ++*n; }
-    if (e == cudaSuccess && (phases & HVP_PHASE_COL)) { e = launch_kind<HVP_COL, D, T>(maps, g, t, s); ++*n; }
+    if (e == cudaSuccess && (phases & HVP_PHASE_ROW)) {
+      e = (g.debug & 8) ? launch_kind<HVP_ROW, D, T>(maps, g, t, s)
+                        : launch_hvp_main(false, D, Pack<T>::kIsBf16, maps, g, t, s);
+      ++*n;
+    }
+    if (e == cudaSuccess && (phases & HVP_PHASE_COL)) {
+      e = (g.debug & 8) ? launch_kind<HVP_COL, D, T>(maps, g, t, s)
+                        : launch_hvp_main(true, D, Pack<T>::kIsBf16, maps, g, t, s);
+      ++*n;
+    }
   }
   return e;
 }
@@ -910,18 +891,8 @@ cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cu
   using namespace tc;
   *err = nullptr;
   TmaMaps maps;
-  memset(&maps, 0, sizeof(maps));
   const int bf = dtype == 1;
-  const void* ptrs[T_COUNT] = {t.Q, t.K, t.V, t.dO, t.g_dQ, t.g_dK, t.g_dV};
-  const int rows[T_COUNT] = {g.N_q, g.N_kv, g.N_kv, g.N_q, g.N_q, g.N_kv, g.N_kv};
-  for (int i = 0; i < T_COUNT; ++i) {
-    const void* p = ptrs[i] ? ptrs[i] : t.Q;   // unused maps still need a valid encoding
-    const int r = ptrs[i] ? rows[i] : g.N_q;
-    if (!encode_map(&maps.m[i], p, bf, g.BH, r, g.D)) {
-      *err = tl_encode_error;
-      return cudaErrorInvalidValue;
-    }
-  }
+  if (!encode_all_maps(&maps, g, t, bf, err)) return cudaErrorInvalidValue;
   if (g.D == 64) {
     return bf ? launch_op<64, __nv_bfloat16>(op, maps, g, t, s, launches, phases)
               : launch_op<64, __half>(op, maps, g, t, s, launches, phases);

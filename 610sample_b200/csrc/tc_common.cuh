@@ -1,0 +1,84 @@
+// Definitions shared by the tensor-core kernel files: tile sizes, warp roles,
+// tensor-map bundle, shared-memory control block and small device helpers.
+#pragma once
+
+#include "attn_common.cuh"
+#include "tc_primitives.cuh"
+
+namespace attn {
+namespace tc {
+
+constexpr int BM = 128;            // stationary rows per CTA
+constexpr int BN = 64;             // streamed rows per iteration
+constexpr int kMathWarps = 8;
+constexpr int kMathThreads = kMathWarps * 32;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kAtomBytesStat = BM * 128;   // [128 rows][64 halves], 16 KB
+constexpr uint32_t kAtomBytesStrm = BN * 128;   // [ 64 rows][64 halves],  8 KB
+constexpr uint32_t kOpTileBytes = BM * 128;     // [128 rows][64 halves], 16 KB
+
+enum Kind { FWD_LSE = 0, FWD_OUT, BWD_ROW, BWD_COL, HVP_PRE, HVP_ROW, HVP_COL };
+enum TensorId { T_Q = 0, T_K, T_V, T_dO, T_gQ, T_gK, T_gV, T_COUNT };
+
+struct TmaMaps { CUtensorMap m[T_COUNT]; };
+
+// Shared-memory control block (lives in the aux area).
+struct Control {
+  uint64_t stat_full;
+  uint64_t stream_full[2];
+  uint64_t stream_empty[2];
+  uint64_t score_full[2];
+  uint64_t score_free[2];
+  uint64_t opnd_full;
+  uint64_t opnd_free;
+  uint64_t acc_done;
+  uint64_t stats_ready[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+// status codes: (kind + 1) << 8 | wait id
+__device__ __forceinline__ uint32_t wait_code(int kind, int id) { return ((uint32_t)(kind + 1) << 8) | (uint32_t)id; }
+
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+  static constexpr int kIsBf16 = 1;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct Pack<__half> {
+  static constexpr int kIsBf16 = 0;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 16 packed halves (two 16-byte chunks) of operand-tile row `row`, columns
+// [col0, col0+16), into a 128-byte-swizzled [128][64] tile.
+__device__ __forceinline__ void store_op16(uint32_t tile, int row, int col0, const uint32_t (&v)[8]) {
+  const uint32_t a0 = tile + sw128_offset(row, col0);
+  const uint32_t a1 = tile + sw128_offset(row, col0 + 8);
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a0), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3])
+               : "memory");
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a1), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+               "r"(v[7])
+               : "memory");
+}
+
+
+
+}  // namespace tc
+}  // namespace attn
