@@ -3,7 +3,7 @@
 // scalars Dv, dot2, dot3 of the pre-pass.
 //
 // Tile shapes and warp roles are those of attn_tc.cu (128 stationary rows, 64
-// streamed rows per step, 8 math warps + TMA warp + MMA warp).  What differs is
+// streamed rows per step, 8 math warps + TMA warp, here with two MMA warps).  What differs is
 // the pipeline, built for the two constraints of this kernel at D = 128 --
 // 512 tensor-memory columns and 227 KB of shared memory:
 //
@@ -39,6 +39,10 @@
 
 namespace attn {
 namespace tc {
+
+constexpr int kMmaWarpA = 9;     // issues everything that touches score region RA
+constexpr int kMmaWarpB = 10;    // issues everything that touches score region RB
+constexpr int kHvpThreads = 352;
 
 struct HvpControl {
   uint64_t stat_full;
@@ -91,7 +95,7 @@ struct HvpCfg {
 };
 
 template <bool COL, int D, typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kHvpThreads, 1)
 hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors t) {
   using CF = HvpCfg<COL, D>;
   constexpr int KIND = CF::kKind;
@@ -118,6 +122,11 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
   float* col_stats = reinterpret_cast<float*>(smem_gen + aux_off + 256);   // [2][4][64], column side only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ATTN_EXPERIMENT
+  const bool dbg_skip_math = (g.debug & 1) != 0, dbg_skip_mma = (g.debug & 2) != 0;
+#else
+  constexpr bool dbg_skip_math = false, dbg_skip_mma = false;
+#endif
   const int n_stat = COL ? g.N_kv : g.N_q;
   const int tiles = (n_stat + BM - 1) / BM;
   const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
@@ -142,21 +151,21 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
     mbar_init(bar_stat_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_stream_full(s), 1);
-      mbar_init(bar_stream_empty(s), 1);
+      mbar_init(bar_stream_empty(s), 2);
       mbar_init(smem_u32(&ctl->stats_ready[s]), kMathWarps);
     }
     mbar_init(bar_ra_full, 1);
     mbar_init(bar_rb_full, 1);
     mbar_init(bar_opa_full, kMathWarps);
     mbar_init(bar_opb_full, kMathWarps);
-    mbar_init(bar_acc_done, 1);
+    mbar_init(bar_acc_done, 2);
     ctl->abort_flag = 0u;
     ctl->tmem_base = 0u;
     fence_barrier_init();
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (warp == kMmaWarp) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+  if (warp == kMmaWarpA) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -199,10 +208,16 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
     }
   }
   // =========================================================================
-  // MMA issuer
+  // MMA issuers.  Warp A owns score region RA (its products and the outputs whose
+  // operands live there), warp B owns RB.  Products issued by one warp execute in
+  // order, which is what makes overwriting a region right after the outputs that
+  // read it safe; the two warps never touch the same columns.  Two issuing warps
+  // are used because one warp cannot issue tcgen05.mma fast enough to keep the
+  // tensor core busy with N <= 128 instructions.
   // =========================================================================
-  else if (warp == kMmaWarp) {
-    if (lane == 0 && n_iter > 0) {
+  else if (warp == kMmaWarpA || warp == kMmaWarpB) {
+    if (n_iter > 0) {
+      const bool is_a = (warp == kMmaWarpA);
       bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
       const uint64_t d_stat = smem_desc_sw128(stat_base, 16, 1024);
       auto stat_desc = [&](int slot, int ks) {   // K-major A from shared memory
@@ -218,89 +233,86 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
       // operand written by the math warps into a 64-column score slot: the 16 elements of
       // k-step ks sit in 8 columns at 32*(ks/2) + 8*(ks%2) (owner half, then chunk)
       auto op_tmem = [&](int col0, int ks) { return tmem_base + (uint32_t)(col0 + 32 * (ks >> 1) + 8 * (ks & 1)); };
+      auto ss = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ss(d, a, b, idesc, acc);
+      };
+      auto ts = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ts(d, a, b, idesc, acc);
+      };
+      auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
       constexpr int KS = D / 16, KO = BN / 16;
       const uint32_t ra = tmem_base + CF::kRA, rb = tmem_base + CF::kRB;
       const uint32_t out0 = tmem_base + CF::kOut0, out1 = tmem_base + CF::kOut1;
 
       auto issue_ra = [&](uint32_t stage) {
-        if constexpr (!COL) {
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S | Q g_dK^T] = Q [K; g_dK]^T
-            mma_ss(ra, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS += g_dQ K^T
-            mma_ss(ra + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
-        } else {
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S^T | K g_dQ^T] = K [Q; g_dQ]^T
-            mma_ss(ra, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS^T += g_dK Q^T
-            mma_ss(ra + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
-        }
+        if (dbg_skip_mma) return;
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S | Q g_dK^T] = Q [K; g_dK]^T   | [S^T | K g_dQ^T] = K [Q; g_dQ]^T
+          ss(ra, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS += g_dQ K^T                 | gdS^T += g_dK Q^T
+          ss(ra + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
       };
       auto issue_rb = [&](uint32_t stage) {
+        if (dbg_skip_mma) return;
         if constexpr (!COL) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [dP | gPdV] = dO [V; g_dV]^T
-            mma_ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
+            ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
         } else {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // dP^T = V dO^T
-            mma_ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
+            ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gPdV^T = g_dV dO^T
-            mma_ss(rb + 64, stat_desc(3, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
+            ss(rb + 64, stat_desc(3, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
         }
       };
       auto issue_out_a = [&](uint32_t stage, bool first) {    // operands living in RA
+        if (dbg_skip_mma) return;
         if constexpr (!COL) {
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_dO += P g_dV
-            mma_ts(out1, op_tmem(CF::kRA, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(first && ks == 0));
+            ts(out1, op_tmem(CF::kRA, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(first && ks == 0));
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_dO += g_dp V
-            mma_ts(out1, op_tmem(CF::kRA + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
+            ts(out1, op_tmem(CF::kRA + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
         } else {
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_V += g_dp^T dO
-            mma_ts(out1, op_tmem(CF::kRA + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, !(first && ks == 0));
+            ts(out1, op_tmem(CF::kRA + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, !(first && ks == 0));
         }
       };
       auto issue_out_b = [&](uint32_t stage, bool first) {    // operands living in RB
+        if (dbg_skip_mma) return;
         _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += dS g_dK      | g_K += dS^T g_dQ
-          mma_ts(out0, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
+          ts(out0, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
         _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += g_S K        | g_K += g_S^T Q
-          mma_ts(out0, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
+          ts(out0, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
       };
 
       if (ok) ok = mbar_wait(bar_stream_full(0), 0, abort_flag, t.status, wait_code(KIND, 3));
+      ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after_sync();
-        issue_ra(strm_base);
-        mma_commit(bar_ra_full);
-        issue_rb(strm_base);
-        mma_commit(bar_rb_full);
+        if (is_a) { issue_ra(strm_base); commit(bar_ra_full); }
+        else { issue_rb(strm_base); commit(bar_rb_full); }
       }
       for (int j = 0; j < n_iter && ok; ++j) {
         const int st = j & 1;
         const uint32_t stage = strm_base + st * CF::kStageBytes;
         const uint32_t nstage = strm_base + (st ^ 1) * CF::kStageBytes;
         const bool more = (j + 1 < n_iter);
-        // half-step 1 of tile j done: RA holds operands
-        ok = mbar_wait(bar_opa_full, j & 1, abort_flag, t.status, wait_code(KIND, 4));
+        // the math warps have written this tile's operands into the region this warp owns
+        ok = mbar_wait(is_a ? bar_opa_full : bar_opb_full, j & 1, abort_flag, t.status, wait_code(KIND, is_a ? 4 : 5));
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        issue_out_a(stage, j == 0);
+        if (is_a) issue_out_a(stage, j == 0); else issue_out_b(stage, j == 0);
+        commit(bar_stream_empty(st));     // this warp's last product reading stage st (two arrivals free it)
         if (more) {
           ok = mbar_wait(bar_stream_full(st ^ 1), ((j + 1) >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_ra(nstage);          // overwrites RA after the outputs above have read it (in-order pipe)
-          mma_commit(bar_ra_full);
-        }
-        // half-step 2 of tile j done: RB holds operands
-        ok = mbar_wait(bar_opb_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_out_b(stage, j == 0);
-        mma_commit(bar_stream_empty(st));   // every product reading this stage has been issued
-        if (more) {
-          issue_rb(nstage);
-          mma_commit(bar_rb_full);
+          // overwrites the region after the outputs above have read it (same warp: in order)
+          if (is_a) { issue_ra(nstage); commit(bar_ra_full); }
+          else { issue_rb(nstage); commit(bar_rb_full); }
         }
       }
-      if (ok) mma_commit(bar_acc_done);
+      if (ok) commit(bar_acc_done);
     }
   }
   // =========================================================================
@@ -319,31 +331,37 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
     if (gidx >= n_stat) { vlo = 0; vhi = 0; }
     const uint32_t vspan = (uint32_t)(vhi - vlo);
 
-    // row side: this thread's query row
-    float rL2 = INFINITY, rDv = 0.f, rD2 = 0.f, rC3 = 0.f;
+    // Per-query-row scalars enter the element algebra negated, so that every use is a
+    // packed add or fused multiply-add:  nL2 = -L*log2(e), nD2 = -dot2, nDv = -Dv,
+    // nC3 = -(dot2*Dv + dot3).  Row side: this thread's own query row (beyond N_q:
+    // nL2 = -inf, which makes p = 0).  Column side: per streamed column, from shared memory.
+    float2 rnL2 = make_float2(-INFINITY, -INFINITY), rnDv = make_float2(0.f, 0.f);
+    float2 rnD2 = make_float2(0.f, 0.f), rnC3 = make_float2(0.f, 0.f);
     if constexpr (!COL) {
       if (gidx < g.N_q) {
-        rL2 = t.L[row_off + gidx] * kLog2e;
-        rDv = t.Dv[row_off + gidx];
-        rD2 = t.dot2[row_off + gidx];
-        rC3 = fmaf(rD2, rDv, t.dot3[row_off + gidx]);
+        const float L2 = t.L[row_off + gidx] * kLog2e, Dv = t.Dv[row_off + gidx];
+        const float d2 = t.dot2[row_off + gidx], c3 = fmaf(d2, Dv, t.dot3[row_off + gidx]);
+        rnL2 = make_float2(-L2, -L2); rnDv = make_float2(-Dv, -Dv);
+        rnD2 = make_float2(-d2, -d2); rnC3 = make_float2(-c3, -c3);
       }
     }
+    const float2 sl2 = make_float2(g.scale_log2e, g.scale_log2e);
+    const float2 sc2 = make_float2(g.scale, g.scale);
 
-    float p_[32], a_[32];   // carried from half-step 1 to half-step 2
+    float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int j0 = (t_begin + it) * BN;
-      const float* cs = col_stats + (it & 1) * 256;   // [L2 | dot2 | Dv | c3] x 64 columns
+      const float* cs = col_stats + (it & 1) * 256;   // [-L2 | -dot2 | -Dv | -c3] x 64 columns
       if constexpr (COL) {
         const int which = threadIdx.x >> 6, c = threadIdx.x & 63;
         const int qi = j0 + c;
-        float v = (which == 0) ? INFINITY : 0.f;
+        float v = (which == 0) ? -INFINITY : 0.f;
         if (qi < g.N_q) {
-          if (which == 0) v = t.L[row_off + qi] * kLog2e;
-          else if (which == 1) v = t.dot2[row_off + qi];
-          else if (which == 2) v = t.Dv[row_off + qi];
-          else v = fmaf(t.dot2[row_off + qi], t.Dv[row_off + qi], t.dot3[row_off + qi]);
+          if (which == 0) v = -t.L[row_off + qi] * kLog2e;
+          else if (which == 1) v = -t.dot2[row_off + qi];
+          else if (which == 2) v = -t.Dv[row_off + qi];
+          else v = -fmaf(t.dot2[row_off + qi], t.Dv[row_off + qi], t.dot3[row_off + qi]);
         }
         col_stats[(it & 1) * 256 + which * 64 + c] = v;
         __syncwarp();
@@ -353,12 +371,16 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
+      // all 32 columns this thread handles in this tile are visible: no per-element predicate
+      const int first = j0 + half * 32;
+      const bool masked = !(first >= vlo && first + 31 < vhi);
 
       // ---------------- half-step 1: RA -> p, a; operands P, g_dp -----------------
       ok = mbar_wait(bar_ra_full, it & 1, abort_flag, t.status, wait_code(KIND, 6));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (!dbg_skip_math)
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const int c0 = half * 32 + ch * 16;
@@ -370,20 +392,24 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
         uint32_t kp[8], kgdp[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          float pp[2], aa[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int cc = c0 + e + u;
-            const bool vis = (uint32_t)(j0 + cc - vlo) < vspan;
-            const float L2 = COL ? cs[cc] : rL2;
-            const float d2 = COL ? cs[64 + cc] : rD2;
-            pp[u] = prob(__uint_as_float(s_[e + u]), g.scale_log2e, L2, vis);
-            aa[u] = fmaf(__uint_as_float(g_[e + u]), g.scale, -d2);
-            p_[ch * 16 + e + u] = pp[u];
-            a_[ch * 16 + e + u] = aa[u];
+          const int cc = c0 + e;
+          float2 nL2 = rnL2, nD2 = rnD2;
+          if constexpr (COL) {
+            nL2 = *reinterpret_cast<const float2*>(cs + cc);
+            nD2 = *reinterpret_cast<const float2*>(cs + 64 + cc);
           }
-          kp[e >> 1] = Pack<T>::pack(pp[0], pp[1]);
-          kgdp[e >> 1] = Pack<T>::pack(pp[0] * aa[0], pp[1] * aa[1]);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(s_[e]), __uint_as_float(s_[e + 1])), sl2, nL2);
+          float2 pp = make_float2(ex2(x.x), ex2(x.y));
+          if (masked) {
+            pp.x = ((uint32_t)(j0 + cc - vlo) < vspan) ? pp.x : 0.f;
+            pp.y = ((uint32_t)(j0 + cc + 1 - vlo) < vspan) ? pp.y : 0.f;
+          }
+          const float2 aa = __ffma2_rn(make_float2(__uint_as_float(g_[e]), __uint_as_float(g_[e + 1])), sc2, nD2);
+          const float2 pa = __fmul2_rn(pp, aa);
+          p_[ch * 8 + (e >> 1)] = pp;
+          a_[ch * 8 + (e >> 1)] = aa;
+          kp[e >> 1] = Pack<T>::pack(pp.x, pp.y);
+          kgdp[e >> 1] = Pack<T>::pack(pa.x, pa.y);
         }
         if constexpr (!COL) tmem_st8(lane_addr + CF::kRA + half * 32 + ch * 8, kp);
         tmem_st8(lane_addr + CF::kRA + 64 + half * 32 + ch * 8, kgdp);
@@ -398,6 +424,7 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (!dbg_skip_math)
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const int c0 = half * 32 + ch * 16;
@@ -409,19 +436,19 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
         uint32_t kds[8], kgs[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          float ds[2], gs[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int cc = c0 + e + u;
-            const float Dv = COL ? cs[128 + cc] : rDv;
-            const float c3 = COL ? cs[192 + cc] : rC3;
-            const float pp = p_[ch * 16 + e + u], aa = a_[ch * 16 + e + u];
-            const float dpd = __uint_as_float(dp_[e + u]) - Dv;
-            ds[u] = pp * dpd;
-            gs[u] = pp * fmaf(aa, dpd, __uint_as_float(gp_[e + u]) - c3);
+          const int cc = c0 + e;
+          float2 nDv = rnDv, nC3 = rnC3;
+          if constexpr (COL) {
+            nDv = *reinterpret_cast<const float2*>(cs + 128 + cc);
+            nC3 = *reinterpret_cast<const float2*>(cs + 192 + cc);
           }
-          kds[e >> 1] = Pack<T>::pack(ds[0], ds[1]);
-          kgs[e >> 1] = Pack<T>::pack(gs[0], gs[1]);
+          const float2 pp = p_[ch * 8 + (e >> 1)], aa = a_[ch * 8 + (e >> 1)];
+          const float2 dpd = __fadd2_rn(make_float2(__uint_as_float(dp_[e]), __uint_as_float(dp_[e + 1])), nDv);
+          const float2 ds = __fmul2_rn(pp, dpd);
+          const float2 tt = __fadd2_rn(make_float2(__uint_as_float(gp_[e]), __uint_as_float(gp_[e + 1])), nC3);
+          const float2 gs = __fmul2_rn(pp, __ffma2_rn(aa, dpd, tt));
+          kds[e >> 1] = Pack<T>::pack(ds.x, ds.y);
+          kgs[e >> 1] = Pack<T>::pack(gs.x, gs.y);
         }
         tmem_st8(lane_addr + CF::kRB + half * 32 + ch * 8, kds);
         tmem_st8(lane_addr + CF::kRB + 64 + half * 32 + ch * 8, kgs);
@@ -474,7 +501,7 @@ hvp_main_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Te
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarpA) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -495,7 +522,7 @@ static cudaError_t launch_one(const TmaMaps& maps, const Geometry& g_in, const T
   auto kern = hvp_main_kernel<COL, D, T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<(unsigned)ctas, kThreads, smem, s>>>(maps, g, t);
+  kern<<<(unsigned)ctas, kHvpThreads, smem, s>>>(maps, g, t);
   return cudaGetLastError();
 }
 
