@@ -132,9 +132,10 @@ std::vector<torch::Tensor> v7_double_backward_cuda(torch::Tensor g_dQ, torch::Te
   auto g_V = torch::empty_like(V);
   auto scratch = torch::empty({(int64_t)(attn_b200_double_backward_scratch_bytes(&s) / sizeof(float)) + 4},
                               Q.options().dtype(torch::kFloat32));
-  const void* O_ptr = O.defined() && O.numel() > 0 ? dense(O).data_ptr() : nullptr;
+  check_like(O, Q, "O");
+  O = dense(O);
   check_rc(attn_b200_double_backward(&s, g_dQ.data_ptr(), g_dK.data_ptr(), g_dV.data_ptr(), dO.data_ptr(),
-                                     Q.data_ptr(), K.data_ptr(), V.data_ptr(), O_ptr, L.data_ptr<float>(),
+                                     Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr<float>(),
                                      g_dO.data_ptr(), g_Q.data_ptr(), g_K.data_ptr(), g_V.data_ptr(),
                                      scratch.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
            "v7_double_backward");

@@ -180,7 +180,7 @@ int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ
   int rc = check_shape(shape);
   if (rc != ATTN_OK) return rc;
   REQUIRE_PTR(g_dQ); REQUIRE_PTR(g_dK); REQUIRE_PTR(g_dV);
-  REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V);
+  REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
   REQUIRE_PTR(g_dO); REQUIRE_PTR(g_Q); REQUIRE_PTR(g_K); REQUIRE_PTR(g_V);
   if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
   if (scratch == nullptr) return fail(ATTN_EINVAL, "scratch is null");

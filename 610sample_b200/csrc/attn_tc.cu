@@ -824,6 +824,8 @@ bool encode_all_maps(TmaMaps* maps, const Geometry& g, const Tensors& t, int is_
 
 cudaError_t launch_hvp_main(bool col, int D, int is_bf16, const TmaMaps& maps, const Geometry& g,
                             const Tensors& t, cudaStream_t s);
+cudaError_t launch_hvp_row(int mode, int D, int is_bf16, const TmaMaps& maps, const Geometry& g,
+                           const Tensors& t, cudaStream_t s);
 
 template <int KIND, int D, typename T>
 static cudaError_t launch_kind(const TmaMaps& maps, const Geometry& g_in, const Tensors& t, cudaStream_t s) {
@@ -867,10 +869,16 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
     if (e == cudaSuccess) e = launch_kind<BWD_COL, D, T>(maps, g, t, s);
     *n = 3;
   } else {
-    if (phases & HVP_PHASE_PRE) { e = launch_kind<HVP_PRE, D, T>(maps, g, t, s); ++*n; }
+    // debug 8 / 16 select earlier generations of the row-side kernels (experiment builds)
+    if (phases & HVP_PHASE_PRE) {
+      e = (g.debug & 24) ? launch_kind<HVP_PRE, D, T>(maps, g, t, s)
+                         : launch_hvp_row(0, D, Pack<T>::kIsBf16, maps, g, t, s);   // scalars + g_dO
+      ++*n;
+    }
     if (e == cudaSuccess && (phases & HVP_PHASE_ROW)) {
       e = (g.debug & 8) ? launch_kind<HVP_ROW, D, T>(maps, g, t, s)
-                        : launch_hvp_main(false, D, Pack<T>::kIsBf16, maps, g, t, s);
+          : (g.debug & 16) ? launch_hvp_main(false, D, Pack<T>::kIsBf16, maps, g, t, s)
+                           : launch_hvp_row(1, D, Pack<T>::kIsBf16, maps, g, t, s);  // g_Q
       ++*n;
     }
     if (e == cudaSuccess && (phases & HVP_PHASE_COL)) {

@@ -1,0 +1,518 @@
+// Row-side kernels of the double backward (Hessian-vector product) on sm_100a.
+//
+// The query side of the HVP needs two [128 x D] fp32 accumulators (g_Q, g_dO).  At
+// D = 128 they would fill half of tensor memory and leave each score region
+// single-buffered, which chains every tensor-core product behind the math warps.
+// The work is therefore split over two kernels with ONE accumulator each, which
+// frees 128 columns to double-buffer the [S | gdS] region:
+//
+//   ROW_PREDO  per-row scalars Dv, dot2, dot3 (to scratch) and
+//                g_dO = P g_dV + (P o gdS) V - dot2 o O
+//              (g_dp = P o (gdS - dot2), and P V = O is an input, so the unknown dot2 is
+//              applied in the epilogue instead of inside the loop)
+//   ROW_Q      g_Q = s (dS g_dK + g_S K), given the scalars
+//
+// Both stream K, g_dK, V, g_dV in 64-row tiles past 128 stationary rows of Q, dO, g_dQ.
+// Tensor memory:  RA0 [0,128) and RA1 [128,256) alternate per tile and hold
+// [S | gdS] = [Q K^T | Q g_dK^T + g_dQ K^T];  RB [256,384) holds [dP | gPdV] =
+// dO [V; g_dV]^T;  OUT [384,384+D).  Per tile the math warps run two half-steps:
+//   half-step 1 reads RA:  p = exp(S - L), and gdS (ROW_PREDO: accumulates dot2, writes
+//               the operands P and P o gdS over the columns it has read) or
+//               a = gdS - dot2 (ROW_Q: nothing written, the buffer is released at once);
+//   half-step 2 reads RB:  ROW_PREDO accumulates Dv, A, E (dot3 = A - 2 Dv dot2 + E);
+//               ROW_Q writes the operands dS = p (dP - Dv) and
+//               g_S = p (a (dP - Dv) + gPdV - c3), c3 = dot2 Dv + dot3, over RB.
+// Output products take their A operand from tensor memory.  Two warps issue MMAs:
+// warp 9 the RA products, warp 10 the RB products and the outputs; one warp alone
+// cannot issue N <= 128 instructions fast enough to keep the tensor core busy.
+// Formulas: reference csrc/flash_double_backward_v7.cu:1257-1454.
+#include "attn_launch.h"
+#include "tc_common.cuh"
+
+namespace attn {
+namespace tc {
+
+enum RowMode { ROW_PREDO = 0, ROW_Q = 1 };
+
+constexpr int kRowMmaWarp1 = 9;     // RA products
+constexpr int kRowMmaWarp2 = 10;    // RB products and output products
+constexpr int kRowThreads = 352;
+
+struct RowControl {
+  uint64_t stat_full;
+  uint64_t stream_full[2];
+  uint64_t stream_empty[2];
+  uint64_t ra_full[2];
+  uint64_t ra_free[2];
+  uint64_t rb_full;
+  uint64_t rb_free;
+  uint64_t op_full;
+  uint64_t acc_done;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+template <int D>
+struct RowCfg {
+  static constexpr int kAtoms = D / 64;
+  static constexpr int kNStat = 3;      // Q, dO, g_dQ
+  static constexpr int kNStream = 4;    // K, g_dK, V, g_dV (pairs back to back)
+  static constexpr uint32_t kStatBytes = kNStat * kAtoms * kAtomBytesStat;
+  static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
+  static constexpr uint32_t kAuxBytes = 256;          // control block
+  static constexpr uint32_t kContentBytes = kStatBytes + 2 * kStageBytes + kAuxBytes;
+  static constexpr uint32_t kMaxSmem = 232448;
+  static_assert(kContentBytes <= kMaxSmem, "shared memory over-subscribed");
+  static constexpr uint32_t kSmemBytes = (kContentBytes + 1024 <= kMaxSmem) ? kContentBytes + 1024 : kMaxSmem;
+  static constexpr int kRA0 = 0, kRB = 256, kOut = 384;
+  static_assert(kOut + D <= kTmemCols, "tensor memory over-subscribed");
+  __host__ __device__ static constexpr uint32_t stream_off(int slot, int atom) {
+    return (uint32_t)(slot >> 1) * (2u * kAtoms * kAtomBytesStrm) + (uint32_t)atom * 2u * kAtomBytesStrm +
+           (uint32_t)(slot & 1) * kAtomBytesStrm;
+  }
+  __host__ __device__ static constexpr int stat_tensor(int slot) { return slot == 0 ? T_Q : slot == 1 ? T_dO : T_gQ; }
+  __host__ __device__ static constexpr int stream_tensor(int slot) {
+    return slot == 0 ? T_K : slot == 1 ? T_gK : slot == 2 ? T_V : T_gV;
+  }
+};
+
+template <int MODE, int D, typename T>
+__global__ void __launch_bounds__(kRowThreads, 1)
+hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors t) {
+  using CF = RowCfg<D>;
+  constexpr int KIND = (MODE == ROW_PREDO) ? HVP_PRE : HVP_ROW;
+  constexpr int kAtoms = CF::kAtoms;
+  constexpr uint32_t kIdesc64 = make_idesc(BM, 64, Pack<T>::kIsBf16, 0, 0);
+  constexpr uint32_t kIdesc128 = make_idesc(BM, 128, Pack<T>::kIsBf16, 0, 0);
+  constexpr uint32_t kIdescOut = make_idesc(BM, D, Pack<T>::kIsBf16, 0, 1);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  {
+    uint32_t dyn_size;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    if (smem_base - smem_u32(smem_raw) + CF::kContentBytes > dyn_size) {   // uniform over the CTA
+      if (threadIdx.x == 0 && t.status != nullptr) atomicCAS(t.status, 0u, wait_code(KIND, 15));
+      return;
+    }
+  }
+  const uint32_t stat_base = smem_base;
+  const uint32_t strm_base = stat_base + CF::kStatBytes;
+  const uint32_t aux_off = CF::kStatBytes + 2 * CF::kStageBytes;
+  RowControl* ctl = reinterpret_cast<RowControl*>(smem_gen + aux_off);
+  // [2 halves][4][128] floats of row sums, exchanged after the last product has read the
+  // stationary tiles: their shared memory is reused
+  float* row_sums = reinterpret_cast<float*>(smem_gen);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles = (g.N_q + BM - 1) / BM;
+  const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
+  const int rank = g.tile_major ? (int)(blockIdx.x / g.BH) : (int)(blockIdx.x - bh * tiles);
+  const int tile = (g.mask_mode != 0) ? rank : (tiles - 1 - rank);   // heavy tiles first
+  const int r0 = tile * BM;
+
+  int lo, hi;
+  key_range_for_queries(g, r0, r0 + BM, lo, hi);
+  const int t_begin = lo / BN;
+  const int n_iter = (hi > lo) ? ((hi + BN - 1) / BN - t_begin) : 0;
+
+  const uint32_t bar_stat_full = smem_u32(&ctl->stat_full);
+  const uint32_t bar_rb_full = smem_u32(&ctl->rb_full), bar_rb_free = smem_u32(&ctl->rb_free);
+  const uint32_t bar_op_full = smem_u32(&ctl->op_full), bar_acc_done = smem_u32(&ctl->acc_done);
+  auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
+  auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
+  auto bar_ra_full = [&](int b) { return smem_u32(&ctl->ra_full[b]); };
+  auto bar_ra_free = [&](int b) { return smem_u32(&ctl->ra_free[b]); };
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_stat_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_stream_full(s), 1);
+      mbar_init(bar_stream_empty(s), 2);                                  // one commit per MMA warp
+      mbar_init(bar_ra_full(s), 1);
+      mbar_init(bar_ra_free(s), MODE == ROW_Q ? kMathWarps : 1);          // math warps | output commit
+    }
+    mbar_init(bar_rb_full, 1);
+    mbar_init(bar_rb_free, kMathWarps);
+    mbar_init(bar_op_full, kMathWarps);
+    mbar_init(bar_acc_done, 1);
+    ctl->abort_flag = 0u;
+    ctl->tmem_base = 0u;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (warp == kRowMmaWarp1) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  // =========================================================================
+  // TMA producer
+  // =========================================================================
+  if (warp == kProducerWarp) {
+    if (lane == 0 && n_iter > 0) {
+      for (int i = 0; i < T_COUNT; ++i) tma_prefetch_desc(&maps.m[i]);
+      mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
+#pragma unroll
+      for (int s = 0; s < CF::kNStat; ++s)
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            tma_load_3d(stat_base + (s * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm,
+                        &maps.m[CF::stat_tensor(s)], a * 64, r0 + h * 64, bh, bar_stat_full);
+      bool ok = true;
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(bar_stream_empty(st), ((it >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
+        const uint32_t stage = strm_base + st * CF::kStageBytes;
+#pragma unroll
+        for (int s = 0; s < CF::kNStream; ++s)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(stage + CF::stream_off(s, a), &maps.m[CF::stream_tensor(s)], a * 64,
+                        (t_begin + it) * BN, bh, bar_stream_full(st));
+      }
+      if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+      }
+    }
+  }
+  // =========================================================================
+  // MMA issuers (converged warps, one elected lane issues)
+  // =========================================================================
+  else if (warp == kRowMmaWarp1 || warp == kRowMmaWarp2) {
+    if (n_iter > 0) {
+      bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
+      ok = __all_sync(0xffffffffu, ok);
+      const uint64_t d_stat = smem_desc_sw128(stat_base, 16, 1024);
+      auto stat_desc = [&](int slot, int ks) {   // K-major A from shared memory
+        return d_stat + (uint64_t)(((slot * kAtoms + (ks >> 2)) * kAtomBytesStat + (ks & 3) * 32) >> 4);
+      };
+      auto strm_desc_k = [&](uint32_t stage, int slot, int ks) {   // K-major B
+        return smem_desc_sw128(stage, 16, 1024) + (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4);
+      };
+      auto strm_desc_mn = [&](uint32_t stage, int slot, int ks) {  // MN-major B, 16 rows per k-step
+        return smem_desc_sw128(stage, 2u * kAtomBytesStrm, 1024) + (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4);
+      };
+      // operand written by the math warps over a 64-column score slot: the 16 elements of
+      // k-step ks sit in 8 columns at 32*(ks/2) + 8*(ks%2) (owner half, then chunk)
+      auto op_tmem = [&](int col0, int ks) { return tmem_base + (uint32_t)(col0 + 32 * (ks >> 1) + 8 * (ks & 1)); };
+      auto ss = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ss(d, a, b, idesc, acc);
+      };
+      auto ts = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ts(d, a, b, idesc, acc);
+      };
+      auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
+      constexpr int KS = D / 16, KO = BN / 16;
+      const uint32_t out = tmem_base + CF::kOut;
+
+      if (warp == kRowMmaWarp1) {
+        // ---- RA products: [S | Q g_dK^T] = Q [K; g_dK]^T, then gdS += g_dQ K^T ----
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int st = j & 1, b = j & 1;
+          const uint32_t stage = strm_base + st * CF::kStageBytes;
+          const uint32_t ra = tmem_base + CF::kRA0 + b * 128;
+          ok = mbar_wait(bar_stream_full(st), (j >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
+          if (ok) ok = mbar_wait(bar_ra_free(b), ((j >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 4));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            ss(ra, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            ss(ra + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+          commit(bar_ra_full(b));
+          commit(bar_stream_empty(st));
+        }
+      } else {
+        // ---- RB products [dP | gPdV] = dO [V; g_dV]^T and the output products ----
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int st = j & 1, b = j & 1;
+          const uint32_t stage = strm_base + st * CF::kStageBytes;
+          const uint32_t rb = tmem_base + CF::kRB;
+          ok = mbar_wait(bar_stream_full(st), (j >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
+          if constexpr (MODE == ROW_PREDO) {
+            // RB holds no operands here: it is free once the math warps have read tile j-1
+            if (ok) ok = mbar_wait(bar_rb_free, (j & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 5));
+          }
+          // ROW_Q: the outputs of tile j-1 read their operands from RB and were issued by this
+          // warp just before, so overwriting RB now is ordered behind them.
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
+          commit(bar_rb_full);
+          ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if constexpr (MODE == ROW_PREDO) {
+            const int ra_col = CF::kRA0 + b * 128;
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += P g_dV
+              ts(out, op_tmem(ra_col, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(j == 0 && ks == 0));
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += (P o gdS) V
+              ts(out, op_tmem(ra_col + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
+            commit(bar_ra_free(b));        // the operands in RA[b] have been consumed
+          } else {
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += dS g_dK
+              ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(j == 0 && ks == 0));
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += g_S K
+              ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
+          }
+          commit(bar_stream_empty(st));
+        }
+        if (ok) commit(bar_acc_done);
+      }
+    }
+  }
+  // =========================================================================
+  // math warps
+  // =========================================================================
+  else {
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const int gidx = r0 + row;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const size_t row_off = (size_t)bh * g.N_q;
+
+    int vlo, vhi;
+    key_range_for_queries(g, gidx, gidx + 1, vlo, vhi);
+    if (gidx >= g.N_q) { vlo = 0; vhi = 0; }
+    const uint32_t vspan = (uint32_t)(vhi - vlo);
+
+    // scalars of this thread's query row, negated so that every use is a packed add / fma
+    float2 nL2 = make_float2(-INFINITY, -INFINITY), nDv = make_float2(0.f, 0.f);
+    float2 nD2 = make_float2(0.f, 0.f), nC3 = make_float2(0.f, 0.f);
+    if (gidx < g.N_q) {
+      const float L2 = t.L[row_off + gidx] * kLog2e;
+      nL2 = make_float2(-L2, -L2);
+      if constexpr (MODE == ROW_Q) {
+        const float Dv = t.Dv[row_off + gidx], d2 = t.dot2[row_off + gidx];
+        const float c3 = fmaf(d2, Dv, t.dot3[row_off + gidx]);
+        nDv = make_float2(-Dv, -Dv); nD2 = make_float2(-d2, -d2); nC3 = make_float2(-c3, -c3);
+      }
+    }
+    const float2 sl2 = make_float2(g.scale_log2e, g.scale_log2e);
+    const float2 sc2 = make_float2(g.scale, g.scale);
+    const float2 zero2 = make_float2(0.f, 0.f);
+
+    float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2 (ROW_PREDO: a_ = p * gdS)
+    float2 acc_D = zero2, acc_2 = zero2, acc_A = zero2, acc_E = zero2;   // ROW_PREDO row sums
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int j0 = (t_begin + it) * BN, b = it & 1;
+      const int first = j0 + half * 32;
+      const bool masked = !(first >= vlo && first + 31 < vhi);
+      const uint32_t ra = lane_addr + CF::kRA0 + b * 128;
+      const uint32_t rb = lane_addr + CF::kRB;
+
+      // ---------------- half-step 1: RA ------------------------------------------
+      ok = mbar_wait(bar_ra_full(b), (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 7));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const int c0 = half * 32 + ch * 16;
+        uint32_t s_[16], g_[16];
+        tmem_ld16(ra + c0, s_);
+        tmem_ld16(ra + 64 + c0, g_);
+        tmem_ld_wait(s_);
+        tmem_ld_wait(g_);
+        uint32_t kp[8], kpg[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const int cc = c0 + e;
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(s_[e]), __uint_as_float(s_[e + 1])), sl2, nL2);
+          float2 pp = make_float2(ex2(x.x), ex2(x.y));
+          if (masked) {
+            pp.x = ((uint32_t)(j0 + cc - vlo) < vspan) ? pp.x : 0.f;
+            pp.y = ((uint32_t)(j0 + cc + 1 - vlo) < vspan) ? pp.y : 0.f;
+          }
+          const float2 gg = make_float2(__uint_as_float(g_[e]), __uint_as_float(g_[e + 1]));
+          p_[ch * 8 + (e >> 1)] = pp;
+          if constexpr (MODE == ROW_PREDO) {
+            const float2 pg = __fmul2_rn(pp, __fmul2_rn(gg, sc2));     // p * gdS
+            a_[ch * 8 + (e >> 1)] = pg;
+            acc_2 = __fadd2_rn(acc_2, pg);
+            kp[e >> 1] = Pack<T>::pack(pp.x, pp.y);
+            kpg[e >> 1] = Pack<T>::pack(pg.x, pg.y);
+          } else {
+            a_[ch * 8 + (e >> 1)] = __ffma2_rn(gg, sc2, nD2);           // gdS - dot2
+          }
+        }
+        if constexpr (MODE == ROW_PREDO) {
+          tmem_st8(ra + half * 32 + ch * 8, kp);
+          tmem_st8(ra + 64 + half * 32 + ch * 8, kpg);
+        }
+      }
+      if constexpr (MODE == ROW_PREDO) {
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_op_full);
+      } else {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ra_free(b));
+      }
+
+      // ---------------- half-step 2: RB ------------------------------------------
+      ok = mbar_wait(bar_rb_full, it & 1, abort_flag, t.status, wait_code(KIND, 8));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const int c0 = half * 32 + ch * 16;
+        uint32_t dp_[16], gp_[16];
+        tmem_ld16(rb + c0, dp_);
+        tmem_ld16(rb + 64 + c0, gp_);
+        tmem_ld_wait(dp_);
+        tmem_ld_wait(gp_);
+        uint32_t kds[8], kgs[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const float2 pp = p_[ch * 8 + (e >> 1)], aa = a_[ch * 8 + (e >> 1)];
+          const float2 dp = make_float2(__uint_as_float(dp_[e]), __uint_as_float(dp_[e + 1]));
+          const float2 gp = make_float2(__uint_as_float(gp_[e]), __uint_as_float(gp_[e + 1]));
+          if constexpr (MODE == ROW_PREDO) {
+            acc_D = __ffma2_rn(pp, dp, acc_D);
+            acc_A = __ffma2_rn(aa, dp, acc_A);
+            acc_E = __ffma2_rn(pp, gp, acc_E);
+          } else {
+            const float2 dpd = __fadd2_rn(dp, nDv);
+            const float2 ds = __fmul2_rn(pp, dpd);
+            const float2 gs = __fmul2_rn(pp, __ffma2_rn(aa, dpd, __fadd2_rn(gp, nC3)));
+            kds[e >> 1] = Pack<T>::pack(ds.x, ds.y);
+            kgs[e >> 1] = Pack<T>::pack(gs.x, gs.y);
+          }
+        }
+        if constexpr (MODE == ROW_Q) {
+          tmem_st8(rb + half * 32 + ch * 8, kds);
+          tmem_st8(rb + 64 + half * 32 + ch * 8, kgs);
+        }
+      }
+      if constexpr (MODE == ROW_Q) {
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_op_full);
+      } else {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rb_free);
+      }
+    }
+
+    // ---------------- results ------------------------------------------------------
+    float dot2_row = 0.f;
+    if constexpr (MODE == ROW_PREDO) {
+      // each row is summed by two threads (column halves): exchange through shared memory
+      float* mine = row_sums + half * 512;
+      const float sD = acc_D.x + acc_D.y, s2 = acc_2.x + acc_2.y, sA = acc_A.x + acc_A.y, sE = acc_E.x + acc_E.y;
+      mine[row] = sD; mine[128 + row] = s2; mine[256 + row] = sA; mine[384 + row] = sE;
+      named_barrier_sync(1, kMathThreads);
+      const float* other = row_sums + (half ^ 1) * 512;
+      const float Dv = sD + other[row], d2 = s2 + other[128 + row];
+      const float A = sA + other[256 + row], E = sE + other[384 + row];
+      dot2_row = d2;
+      if (half == 0 && gidx < g.N_q) {
+        t.Dv[row_off + gidx] = Dv;
+        t.dot2[row_off + gidx] = d2;
+        t.dot3[row_off + gidx] = A - 2.f * Dv * d2 + E;
+      }
+    }
+    if (n_iter > 0 && ok) ok = mbar_wait(bar_acc_done, 0, abort_flag, t.status, wait_code(KIND, 9));
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after_sync();
+    constexpr int kColsPerHalf = D / 2;
+    T* dst = (T*)(MODE == ROW_PREDO ? t.out_g_dO : t.out_g_Q);
+    const float mul = (MODE == ROW_PREDO) ? 1.f : g.scale;
+    const size_t elem0 = ((size_t)bh * g.N_q + gidx) * D + half * kColsPerHalf;
+#pragma unroll
+    for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
+      uint32_t v[16];
+      if (n_iter > 0 && ok) {
+        tmem_ld16(lane_addr + CF::kOut + half * kColsPerHalf + ch * 16, v);
+        tmem_ld_wait(v);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = 0u;
+      }
+      if (gidx < g.N_q) {
+        float f[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]) * mul;
+        if constexpr (MODE == ROW_PREDO) {
+          // g_dO = g_dO' - dot2 * O  (P V = O)
+          const T* orow = (const T*)t.O + elem0 + ch * 16;
+          const uint4 o0 = reinterpret_cast<const uint4*>(orow)[0], o1 = reinterpret_cast<const uint4*>(orow)[1];
+          const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 of = Pack<T>::unpack(ow[e]);
+            f[2 * e] = fmaf(-dot2_row, of.x, f[2 * e]);
+            f[2 * e + 1] = fmaf(-dot2_row, of.y, f[2 * e + 1]);
+          }
+        }
+        uint4 w0, w1;
+        w0.x = Pack<T>::pack(f[0], f[1]);   w0.y = Pack<T>::pack(f[2], f[3]);
+        w0.z = Pack<T>::pack(f[4], f[5]);   w0.w = Pack<T>::pack(f[6], f[7]);
+        w1.x = Pack<T>::pack(f[8], f[9]);   w1.y = Pack<T>::pack(f[10], f[11]);
+        w1.z = Pack<T>::pack(f[12], f[13]); w1.w = Pack<T>::pack(f[14], f[15]);
+        reinterpret_cast<uint4*>(dst + elem0 + ch * 16)[0] = w0;
+        reinterpret_cast<uint4*>(dst + elem0 + ch * 16)[1] = w1;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kRowMmaWarp1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int MODE, int D, typename T>
+static cudaError_t launch_row(const TmaMaps& maps, const Geometry& g_in, const Tensors& t, cudaStream_t s) {
+  using CF = RowCfg<D>;
+  Geometry g = g_in;
+  const long long ctas = (long long)g.BH * ((g.N_q + BM - 1) / BM);
+  if (ctas <= 0) return cudaSuccess;
+  if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  g.tile_major = ctas < 8 * 148 ? 1 : 0;
+  // more than half of an SM's shared memory: one CTA per SM, so the 512-column
+  // tensor-memory allocation never waits for a co-resident CTA
+  const size_t smem = CF::kSmemBytes < 122880u ? 122880u : CF::kSmemBytes;
+  auto kern = hvp_row_kernel<MODE, D, T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<(unsigned)ctas, kRowThreads, smem, s>>>(maps, g, t);
+  return cudaGetLastError();
+}
+
+// mode 0: per-row scalars + g_dO;  mode 1: g_Q
+cudaError_t launch_hvp_row(int mode, int D, int is_bf16, const TmaMaps& maps, const Geometry& g,
+                           const Tensors& t, cudaStream_t s) {
+  if (mode == 0) {
+    if (D == 64) return is_bf16 ? launch_row<ROW_PREDO, 64, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_PREDO, 64, __half>(maps, g, t, s);
+    return is_bf16 ? launch_row<ROW_PREDO, 128, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_PREDO, 128, __half>(maps, g, t, s);
+  }
+  if (D == 64) return is_bf16 ? launch_row<ROW_Q, 64, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_Q, 64, __half>(maps, g, t, s);
+  return is_bf16 ? launch_row<ROW_Q, 128, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_Q, 128, __half>(maps, g, t, s);
+}
+
+}  // namespace tc
+}  // namespace attn

@@ -87,8 +87,8 @@ size_t attn_b200_double_backward_scratch_bytes(const attn_shape_t* shape);
 /* Double backward (Hessian-vector product).  Given tangents g_dQ, g_dK, g_dV
  * on the first backward's outputs, returns the gradients with respect to dO, Q,
  * K and V (O and L are treated as functions of Q, K, V).  The N_q x N_kv score
- * matrix is never materialised.  `O` is accepted for signature parity and may
- * be NULL: D_i is recomputed as sum_j P*dP in float32.
+ * matrix is never materialised.  D_i is recomputed as sum_j P*dP in float32; the
+ * saved O enters only as P V in g_dO = P g_dV + (P o gdS) V - dot2 o O.
  * Replaces v7_double_backward_cuda (reference :1815-1842, kernels :1145-1702);
  * output order as :1809. */
 int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const void* g_dK,
@@ -98,7 +98,7 @@ int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const
 
 /* The same computation restricted to some of its kernels, for profiling one
  * kernel at a time: `phases` is a bit mask of 1 (per-row scalars Dv, dot2, dot3
- * into scratch), 2 (g_Q and g_dO; needs the scalars in scratch) and 4 (g_K and
+ * into scratch, and g_dO), 2 (g_Q; needs the scalars in scratch) and 4 (g_K and
  * g_V; needs the scalars too).  7 is attn_b200_double_backward.  The reference
  * splits its double backward the same way into kernel A (rows, two passes) and
  * kernel B (columns), csrc/flash_double_backward_v7.cu:1778-1807. */
