@@ -41,8 +41,8 @@ sys.path.insert(0, ROOT)
 WORKLOAD = dict(name="hvp_bf16_causal_B4_H16_N4096_D128", B=4, H=16, N=4096, D=128,
                 window_size=4096, chunk_id=0, mask_mode=0)
 HVP_GEMMS = 12          # algorithmic contractions of the double backward
-ROW_KERNEL_GEMMS = 9    # contractions the row kernel executes (5 score + 4 output)
-PRE_KERNEL_GEMMS = 5
+ROW_KERNEL_GEMMS = 7    # contractions the g_Q kernel executes (5 score + 2 output)
+PRE_KERNEL_GEMMS = 7    # scalars + g_dO kernel (5 score + 2 output)
 COL_KERNEL_GEMMS = 8
 
 
