@@ -16,11 +16,13 @@ ATTN_F16, ATTN_BF16, ATTN_F32 = 0, 1, 2
 MASK_REFERENCE, MASK_NONE = 0, 1
 IMPL_AUTO, IMPL_SIMT, IMPL_TENSOR = 0, 1, 2
 ATTN_OK = 0
+ATTN_ETOOLARGE = -5
+STATIC_SCRATCH_ROWS = 1 << 20
 
 EXPORTS = (
     "attn_b200_forward", "attn_b200_backward_scratch_bytes", "attn_b200_backward",
     "attn_b200_double_backward_scratch_bytes", "attn_b200_double_backward",
-    "attn_b200_double_backward_phases",
+    "attn_b200_double_backward_phases", "attn_b200_double_backward_static",
     "attn_b200_last_launch_count", "attn_b200_device_status", "attn_b200_last_error",
     "attn_b200_version", "attn_b200_selftest_gemm",
 )
@@ -49,6 +51,7 @@ def lib() -> C.CDLL:
         L.attn_b200_double_backward_scratch_bytes.restype = C.c_size_t
         L.attn_b200_double_backward.argtypes = [C.POINTER(Shape)] + [vp] * 13 + [fp, vp]
         L.attn_b200_double_backward_phases.argtypes = [C.POINTER(Shape)] + [vp] * 13 + [fp, vp, C.c_int32]
+        L.attn_b200_double_backward_static.argtypes = [C.POINTER(Shape)] + [vp] * 13 + [vp]
         L.attn_b200_device_status.argtypes = [C.POINTER(C.c_uint32)]
         L.attn_b200_last_error.restype = C.c_char_p
         L.attn_b200_version.restype = C.c_char_p

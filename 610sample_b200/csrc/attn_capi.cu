@@ -196,6 +196,99 @@ int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ
   return run(attn::OP_DOUBLE_BACKWARD, shape, t, stream, phases);
 }
 
+// ---------------------------------------------------------------------------
+// Double backward for callers that must not allocate
+// ---------------------------------------------------------------------------
+namespace {
+
+// Per-row scalars (Dv, dot2, dot3) of the double backward for at most
+// ATTN_B200_STATIC_SCRATCH_ROWS query rows in total (B * H * N_q), 12 MB.  The array
+// belongs to the loaded library image: every GPU that loads the library holds its own
+// copy until the process exits.
+static __device__ __align__(256) float g_static_hvp_scratch[3 * ATTN_B200_STATIC_SCRATCH_ROWS];
+
+// Device address of the array per device.  In host code the name of a __device__
+// variable is only a handle; a kernel needs the address cudaGetSymbolAddress returns
+// while the device in question is current.
+float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+int static_scratch_pointer(int dev, float** out) {
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_hvp_scratch);
+    if (e != cudaSuccess)
+      return fail(ATTN_ECUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_scratch_ptr[dev];
+  return ATTN_OK;
+}
+
+}  // namespace
+
+int attn_b200_double_backward_static(const attn_shape_t* shape, const void* g_dQ, const void* g_dK,
+                                     const void* g_dV, const void* dO, const void* Q, const void* K,
+                                     const void* V, const void* O, const float* L, void* g_dO, void* g_Q,
+                                     void* g_K, void* g_V, void* stream) {
+  int rc = check_shape(shape);
+  if (rc != ATTN_OK) return rc;
+  REQUIRE_PTR(g_dQ); REQUIRE_PTR(g_dK); REQUIRE_PTR(g_dV);
+  REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
+  REQUIRE_PTR(g_dO); REQUIRE_PTR(g_Q); REQUIRE_PTR(g_K); REQUIRE_PTR(g_V);
+  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
+  const long long rows = (long long)shape->B * shape->H * shape->N_q;
+  if (rows > (long long)ATTN_B200_STATIC_SCRATCH_ROWS)
+    return fail(ATTN_ETOOLARGE,
+                "B*H*N_q = %lld query rows exceed the built-in scratch of %d rows; use "
+                "attn_b200_double_backward with caller-provided scratch",
+                rows, (int)ATTN_B200_STATIC_SCRATCH_ROWS);
+  tl_launches = 0;
+  const attn::Geometry g = make_geometry(shape);
+  if (g.BH == 0 || (g.N_q == 0 && g.N_kv == 0)) return ATTN_OK;
+
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ATTN_EINVAL, "device index %d out of range", dev);
+  // Makes the device's primary context current on this host thread (tensor-map encoding
+  // is a driver call) without touching the allocator.
+  e = cudaSetDevice(dev);
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  float* scratch = nullptr;
+  rc = static_scratch_pointer(dev, &scratch);
+  if (rc != ATTN_OK) return rc;
+
+  attn::Tensors t;
+  memset(&t, 0, sizeof(t));
+  t.g_dQ = g_dQ; t.g_dK = g_dK; t.g_dV = g_dV;
+  t.dO = dO; t.Q = Q; t.K = K; t.V = V; t.O = O; t.L = L;
+  t.out_g_dO = g_dO; t.out_g_Q = g_Q; t.out_g_K = g_K; t.out_g_V = g_V;
+  // Nothing in the scratch has to start at zero: the first kernel writes all three
+  // scalars of every row in range before the later kernels read them.
+  t.Dv = scratch;
+  t.dot2 = scratch + (size_t)rows;
+  t.dot3 = scratch + 2 * (size_t)rows;
+  rc = status_pointer(&t.status);
+  if (rc != ATTN_OK) return rc;
+
+  const bool use_tc = shape->impl == ATTN_IMPL_TENSOR ||
+                      (shape->impl == ATTN_IMPL_AUTO && attn::tc_supported(shape->dtype, shape->D));
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (use_tc) {
+    const char* why = nullptr;
+    e = attn::launch_tc(attn::OP_DOUBLE_BACKWARD, shape->dtype, g, t, cs, &tl_launches, &why, attn::HVP_PHASE_ALL);
+    if (e != cudaSuccess)
+      return fail(ATTN_ECUDA, "tensor-core launch failed: %s%s%s", cudaGetErrorString(e), why ? ": " : "", why ? why : "");
+  } else {
+    e = attn::launch_simt(attn::OP_DOUBLE_BACKWARD, shape->dtype, g, t, cs, &tl_launches, attn::HVP_PHASE_ALL);
+    if (e != cudaSuccess) return fail(ATTN_ECUDA, "SIMT launch failed: %s", cudaGetErrorString(e));
+  }
+  tl_error[0] = 0;
+  return ATTN_OK;
+}
+
 int attn_b200_last_launch_count(void) { return tl_launches; }
 
 int attn_b200_device_status(uint32_t* code) {

@@ -68,6 +68,20 @@ def double_backward_phases(g_dQ, g_dK, g_dV, dO, Q, K, V, O, L, window_size, chu
     return out
 
 
+def double_backward_static(g_dQ, g_dK, g_dV, dO, Q, K, V, O, L, window_size, chunk_id, mask_mode=0, impl=0, out=None):
+    """The allocation-free entry point: the scratch is the library's built-in array.  The four
+    outputs must be passed in (`out`) by a caller that really cannot allocate; they are created
+    here only when omitted."""
+    s = _shape(Q, K, window_size, chunk_id, mask_mode, impl)
+    if out is None:
+        out = (torch.empty_like(Q), torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V))
+    g_dO, g_Q, g_K, g_V = out
+    capi.check(capi.lib().attn_b200_double_backward_static(
+        s, _p(g_dQ), _p(g_dK), _p(g_dV), _p(dO), _p(Q), _p(K), _p(V), _p(O), _p(L),
+        _p(g_dO), _p(g_Q), _p(g_K), _p(g_V), _stream()), "attn_b200_double_backward_static")
+    return out
+
+
 def selftest_gemm(A, B, N, K, flags):
     Cout = torch.zeros(128, N, dtype=torch.float32, device=A.device)
     capi.check(capi.lib().attn_b200_selftest_gemm(_p(A), _p(B), _p(Cout), N, K, _DT[A.dtype], flags, _stream()),

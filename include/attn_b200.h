@@ -108,6 +108,36 @@ int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ
                                      void* g_Q, void* g_K, void* g_V, float* scratch, void* stream,
                                      int32_t phases);
 
+/* Double backward without any allocation: same inputs, outputs and results as
+ * attn_b200_double_backward, but the per-row scratch lives in a fixed array inside
+ * the library instead of being passed in.  It has no counterpart in the reference
+ * (whose launcher allocates its scratch through ATen on every call).
+ *
+ * Who needs it: code that may not call an allocator where the kernel is launched --
+ * a host thread inside a real-time or interrupt-like section, a plugin whose host
+ * application owns all device memory and forbids cudaMalloc after start-up, a
+ * runtime whose memory plan is frozen before execution begins.  This call issues no
+ * cudaMalloc / cudaFree and no allocating library routine; the caller still owns Q,
+ * K, V, ..., and the four outputs.
+ *
+ * Limit: B * H * N_q <= ATTN_B200_STATIC_SCRATCH_ROWS (1,048,576 query rows; the
+ * array is 12 MB and each GPU that loads the library keeps its copy until the process
+ * exits).  Larger problems are rejected with ATTN_ETOOLARGE before anything is
+ * launched; use attn_b200_double_backward with your own scratch for those.
+ *
+ * The first call on a device looks up the device address of the array (one
+ * cudaGetSymbolAddress, cached afterwards).  Make that first call outside any stream
+ * capture.  All calls on one device share the one array and it keeps whatever the
+ * last call left there; nothing in it needs clearing, since each call rewrites every
+ * value it later reads.  Because of the sharing, two calls whose kernels can overlap
+ * on the GPU (different streams, or different host threads) race on the scratch and
+ * corrupt each other: keep calls on one device ordered on one stream. */
+#define ATTN_B200_STATIC_SCRATCH_ROWS (1 << 20)
+int attn_b200_double_backward_static(const attn_shape_t* shape, const void* g_dQ, const void* g_dK,
+                                     const void* g_dV, const void* dO, const void* Q, const void* K,
+                                     const void* V, const void* O, const float* L, void* g_dO,
+                                     void* g_Q, void* g_K, void* g_V, void* stream);
+
 /* Number of kernels the last successful call of the calling thread launched. */
 int attn_b200_last_launch_count(void);
 
