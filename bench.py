@@ -44,6 +44,10 @@ HVP_GEMMS = 12          # algorithmic contractions of the double backward
 ROW_KERNEL_GEMMS = 7    # contractions the g_Q kernel executes (5 score + 2 output)
 PRE_KERNEL_GEMMS = 7    # scalars + g_dO kernel (5 score + 2 output)
 COL_KERNEL_GEMMS = 8
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture at 16 (batch, head)
+# slices (profiles/hvp_kernels_bf16_causal_N4096_D128_16heads_ncu_full.md); traffic grows in
+# proportion to the number of slices, so the bench scales it by BH / 16.
+NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 196.3e6, "row": 173.4e6, "col": 134.6e6}
 
 
 def visible_pairs_causal(n: int) -> int:
@@ -313,7 +317,9 @@ def run_ours(args):
             dom = max(phase_ms, key=phase_ms.get)
             ach = 2.0 * D * k_flops[dom] * pairs / (phase_ms[dom] * 1e-3) / 1e12
             line["roofline"] = {"bound": "tensor", "kernel": "hvp_" + dom, "achieved": ach, "peak": peaks["bf16_tflops"],
-                                "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "traffic": None,
+                                "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
+                                "traffic": NCU_TRAFFIC_BYTES_16_SLICES[dom] * BH / 16.0,
+                                "traffic_note": "bytes per launch, scaled from an ncu capture at 16 slices",
                                 "peak_source": peaks["source"],
                                 "kernel_ms": phase_ms, "gemms_counted": k_flops[dom]}
         if world == 1 and not args.no_cpu_baseline:
