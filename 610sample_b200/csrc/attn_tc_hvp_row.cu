@@ -12,19 +12,24 @@
 //              applied in the epilogue instead of inside the loop)
 //   ROW_Q      g_Q = s (dS g_dK + g_S K), given the scalars
 //
-// Both stream K, g_dK, V, g_dV in 64-row tiles past 128 stationary rows of Q, dO, g_dQ.
-// Tensor memory:  RA0 [0,128) and RA1 [128,256) alternate per tile and hold
-// [S | gdS] = [Q K^T | Q g_dK^T + g_dQ K^T];  RB [256,384) holds [dP | gPdV] =
-// dO [V; g_dV]^T;  OUT [384,384+D).  Per tile the math warps run two half-steps:
-//   half-step 1 reads RA:  p = exp(S - L), and gdS (ROW_PREDO: accumulates dot2, writes
-//               the operands P and P o gdS over the columns it has read) or
-//               a = gdS - dot2 (ROW_Q: nothing written, the buffer is released at once);
-//   half-step 2 reads RB:  ROW_PREDO accumulates Dv, A, E (dot3 = A - 2 Dv dot2 + E);
-//               ROW_Q writes the operands dS = p (dP - Dv) and
+// Both stream K, g_dK, V, g_dV in 64-row tiles (three TMA stages) past 128 stationary
+// rows of Q, dO, g_dQ.  Q and dO are copied once into TENSOR MEMORY and used from there
+// as the A operand of their score products (a stationary operand in shared memory is
+// re-read by every MMA instruction, and shared-memory operand bandwidth is what limits
+// these kernels); g_dQ stays in shared memory.
+// Tensor memory:  RA [0,128) = [S | gdS] = [Q K^T | Q g_dK^T + g_dQ K^T];
+// RB [128,256) = [dP | gPdV] = dO [V; g_dV]^T;  OUT [256,256+D);  Q at [384,384+D/2),
+// dO at [448,448+D/2) (two halves per 32-bit column).  Per tile the math warps run two
+// half-steps:
+//   half-step 1 reads RA:  p = exp(S - L) and either p*gdS (ROW_PREDO, accumulating dot2)
+//               or a = gdS - dot2 (ROW_Q); both are kept in registers and RA is released at once;
+//   half-step 2 reads RB:  ROW_PREDO accumulates Dv, A, E (dot3 = A - 2 Dv dot2 + E) and
+//               writes the operands P and P o gdS over RB; ROW_Q writes dS = p (dP - Dv) and
 //               g_S = p (a (dP - Dv) + gPdV - c3), c3 = dot2 Dv + dot3, over RB.
-// Output products take their A operand from tensor memory.  Two warps issue MMAs:
-// warp 9 the RA products, warp 10 the RB products and the outputs; one warp alone
-// cannot issue N <= 128 instructions fast enough to keep the tensor core busy.
+// Output products take their A operand from RB.  Two warps issue MMAs: warp 9 the RA
+// products, warp 10 the RB products and the outputs (in order, so RB is overwritten only
+// after the outputs that read it); one warp alone cannot issue N <= 128 instructions fast
+// enough to keep the tensor core busy.
 // Formulas: reference csrc/flash_double_backward_v7.cu:1257-1454.
 #include "attn_launch.h"
 #include "tc_common.cuh"
@@ -38,14 +43,17 @@ constexpr int kRowMmaWarp1 = 9;     // RA products
 constexpr int kRowMmaWarp2 = 10;    // RB products and output products
 constexpr int kRowThreads = 352;
 
+constexpr int kRowStages = 3;
+
 struct RowControl {
-  uint64_t stat_full;
-  uint64_t stream_full[2];
-  uint64_t stream_empty[2];
-  uint64_t ra_full[2];
-  uint64_t ra_free[2];
+  uint64_t stat_full;          // g_dQ tile in shared memory
+  uint64_t staging_full;       // Q and dO tiles in the staging buffer (stage 2)
+  uint64_t stat_tmem_ready;    // Q and dO copied to tensor memory
+  uint64_t stream_full[kRowStages];
+  uint64_t stream_empty[kRowStages];
+  uint64_t ra_full;
+  uint64_t ra_free;
   uint64_t rb_full;
-  uint64_t rb_free;
   uint64_t op_full;
   uint64_t acc_done;
   uint32_t tmem_base;
@@ -55,22 +63,21 @@ struct RowControl {
 template <int D>
 struct RowCfg {
   static constexpr int kAtoms = D / 64;
-  static constexpr int kNStat = 3;      // Q, dO, g_dQ
   static constexpr int kNStream = 4;    // K, g_dK, V, g_dV (pairs back to back)
-  static constexpr uint32_t kStatBytes = kNStat * kAtoms * kAtomBytesStat;
+  static constexpr uint32_t kStatBytes = kAtoms * kAtomBytesStat;            // g_dQ only
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
+  static_assert(kStageBytes == 2 * kAtoms * kAtomBytesStat, "Q and dO are staged in one stream stage");
   static constexpr uint32_t kAuxBytes = 256;          // control block
-  static constexpr uint32_t kContentBytes = kStatBytes + 2 * kStageBytes + kAuxBytes;
+  static constexpr uint32_t kContentBytes = kStatBytes + kRowStages * kStageBytes + kAuxBytes;
   static constexpr uint32_t kMaxSmem = 232448;
   static_assert(kContentBytes <= kMaxSmem, "shared memory over-subscribed");
   static constexpr uint32_t kSmemBytes = (kContentBytes + 1024 <= kMaxSmem) ? kContentBytes + 1024 : kMaxSmem;
-  static constexpr int kRA0 = 0, kRB = 256, kOut = 384;
-  static_assert(kOut + D <= kTmemCols, "tensor memory over-subscribed");
+  static constexpr int kRA = 0, kRB = 128, kOut = 256, kQT = 384, kDOT = 448;
+  static_assert(kOut + D <= kQT && kQT + D / 2 <= kDOT && kDOT + D / 2 <= kTmemCols, "tensor memory over-subscribed");
   __host__ __device__ static constexpr uint32_t stream_off(int slot, int atom) {
     return (uint32_t)(slot >> 1) * (2u * kAtoms * kAtomBytesStrm) + (uint32_t)atom * 2u * kAtomBytesStrm +
            (uint32_t)(slot & 1) * kAtomBytesStrm;
   }
-  __host__ __device__ static constexpr int stat_tensor(int slot) { return slot == 0 ? T_Q : slot == 1 ? T_dO : T_gQ; }
   __host__ __device__ static constexpr int stream_tensor(int slot) {
     return slot == 0 ? T_K : slot == 1 ? T_gK : slot == 2 ? T_V : T_gV;
   }
@@ -99,10 +106,11 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   }
   const uint32_t stat_base = smem_base;
   const uint32_t strm_base = stat_base + CF::kStatBytes;
-  const uint32_t aux_off = CF::kStatBytes + 2 * CF::kStageBytes;
+  const uint32_t aux_off = CF::kStatBytes + kRowStages * CF::kStageBytes;
+  const uint32_t staging = strm_base + 2 * CF::kStageBytes;   // Q then dO, before the third stage is used
   RowControl* ctl = reinterpret_cast<RowControl*>(smem_gen + aux_off);
   // [2 halves][4][128] floats of row sums, exchanged after the last product has read the
-  // stationary tiles: their shared memory is reused
+  // g_dQ tile: its shared memory is reused
   float* row_sums = reinterpret_cast<float*>(smem_gen);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,23 +126,25 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const int n_iter = (hi > lo) ? ((hi + BN - 1) / BN - t_begin) : 0;
 
   const uint32_t bar_stat_full = smem_u32(&ctl->stat_full);
-  const uint32_t bar_rb_full = smem_u32(&ctl->rb_full), bar_rb_free = smem_u32(&ctl->rb_free);
+  const uint32_t bar_staging_full = smem_u32(&ctl->staging_full);
+  const uint32_t bar_stat_tmem_ready = smem_u32(&ctl->stat_tmem_ready);
+  const uint32_t bar_ra_full = smem_u32(&ctl->ra_full), bar_ra_free = smem_u32(&ctl->ra_free);
+  const uint32_t bar_rb_full = smem_u32(&ctl->rb_full);
   const uint32_t bar_op_full = smem_u32(&ctl->op_full), bar_acc_done = smem_u32(&ctl->acc_done);
   auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
   auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
-  auto bar_ra_full = [&](int b) { return smem_u32(&ctl->ra_full[b]); };
-  auto bar_ra_free = [&](int b) { return smem_u32(&ctl->ra_free[b]); };
 
   if (threadIdx.x == 0) {
     mbar_init(bar_stat_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    mbar_init(bar_staging_full, 1);
+    mbar_init(bar_stat_tmem_ready, kMathWarps);
+    for (int s = 0; s < kRowStages; ++s) {
       mbar_init(bar_stream_full(s), 1);
-      mbar_init(bar_stream_empty(s), 2);                                  // one commit per MMA warp
-      mbar_init(bar_ra_full(s), 1);
-      mbar_init(bar_ra_free(s), MODE == ROW_Q ? kMathWarps : 1);          // math warps | output commit
+      mbar_init(bar_stream_empty(s), 2);      // one commit per MMA warp
     }
+    mbar_init(bar_ra_full, 1);
+    mbar_init(bar_ra_free, kMathWarps);
     mbar_init(bar_rb_full, 1);
-    mbar_init(bar_rb_free, kMathWarps);
     mbar_init(bar_op_full, kMathWarps);
     mbar_init(bar_acc_done, 1);
     ctl->abort_flag = 0u;
@@ -157,18 +167,24 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     if (lane == 0 && n_iter > 0) {
       for (int i = 0; i < T_COUNT; ++i) tma_prefetch_desc(&maps.m[i]);
       mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
+      mbar_arrive_expect_tx(bar_staging_full, CF::kStageBytes);
 #pragma unroll
-      for (int s = 0; s < CF::kNStat; ++s)
+      for (int a = 0; a < kAtoms; ++a)
 #pragma unroll
-        for (int a = 0; a < kAtoms; ++a)
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-            tma_load_3d(stat_base + (s * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm,
-                        &maps.m[CF::stat_tensor(s)], a * 64, r0 + h * 64, bh, bar_stat_full);
+        for (int h = 0; h < 2; ++h) {
+          tma_load_3d(stat_base + a * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[T_gQ], a * 64, r0 + h * 64, bh,
+                      bar_stat_full);
+          tma_load_3d(staging + a * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[T_Q], a * 64, r0 + h * 64, bh,
+                      bar_staging_full);
+          tma_load_3d(staging + (kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[T_dO], a * 64,
+                      r0 + h * 64, bh, bar_staging_full);
+        }
       bool ok = true;
       for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1;
-        ok = mbar_wait(bar_stream_empty(st), ((it >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
+        const int st = it % kRowStages;
+        ok = mbar_wait(bar_stream_empty(st), ((it / kRowStages) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
+        // the third stage doubles as the staging buffer of Q and dO until they are in tensor memory
+        if (ok && it == 2) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 10));
         if (!ok) break;
         mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
         const uint32_t stage = strm_base + st * CF::kStageBytes;
@@ -191,10 +207,12 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   else if (warp == kRowMmaWarp1 || warp == kRowMmaWarp2) {
     if (n_iter > 0) {
       bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
+      if (ok) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 11));
       ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after_sync();
       const uint64_t d_stat = smem_desc_sw128(stat_base, 16, 1024);
-      auto stat_desc = [&](int slot, int ks) {   // K-major A from shared memory
-        return d_stat + (uint64_t)(((slot * kAtoms + (ks >> 2)) * kAtomBytesStat + (ks & 3) * 32) >> 4);
+      auto gq_desc = [&](int ks) {   // K-major A from shared memory: the g_dQ tile
+        return d_stat + (uint64_t)(((ks >> 2) * kAtomBytesStat + (ks & 3) * 32) >> 4);
       };
       auto strm_desc_k = [&](uint32_t stage, int slot, int ks) {   // K-major B
         return smem_desc_sw128(stage, 16, 1024) + (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4);
@@ -214,55 +232,49 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
       constexpr int KS = D / 16, KO = BN / 16;
       const uint32_t out = tmem_base + CF::kOut;
+      const uint32_t ra = tmem_base + CF::kRA, rb = tmem_base + CF::kRB;
+      const uint32_t qt = tmem_base + CF::kQT, dot = tmem_base + CF::kDOT;
 
       if (warp == kRowMmaWarp1) {
-        // ---- RA products: [S | Q g_dK^T] = Q [K; g_dK]^T, then gdS += g_dQ K^T ----
+        // ---- RA products: [S | Q g_dK^T] = Q [K; g_dK]^T (Q from tensor memory), gdS += g_dQ K^T ----
         for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j & 1, b = j & 1;
+          const int st = j % kRowStages;
           const uint32_t stage = strm_base + st * CF::kStageBytes;
-          const uint32_t ra = tmem_base + CF::kRA0 + b * 128;
-          ok = mbar_wait(bar_stream_full(st), (j >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
-          if (ok) ok = mbar_wait(bar_ra_free(b), ((j >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 4));
+          ok = mbar_wait(bar_stream_full(st), (j / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
+          if (ok) ok = mbar_wait(bar_ra_free, (j & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 4));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-            ss(ra, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
+            ts(ra, qt + 8 * ks, strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-            ss(ra + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
-          commit(bar_ra_full(b));
+            ss(ra + 64, gq_desc(ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+          commit(bar_ra_full);
           commit(bar_stream_empty(st));
         }
       } else {
-        // ---- RB products [dP | gPdV] = dO [V; g_dV]^T and the output products ----
+        // ---- RB products [dP | gPdV] = dO [V; g_dV]^T (dO from tensor memory) and the outputs.
+        // The outputs of tile j read their operands from RB and are issued by this warp before
+        // the RB products of tile j+1, so RB is overwritten only after they have read it.
         for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j & 1, b = j & 1;
+          const int st = j % kRowStages;
           const uint32_t stage = strm_base + st * CF::kStageBytes;
-          const uint32_t rb = tmem_base + CF::kRB;
-          ok = mbar_wait(bar_stream_full(st), (j >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
-          if constexpr (MODE == ROW_PREDO) {
-            // RB holds no operands here: it is free once the math warps have read tile j-1
-            if (ok) ok = mbar_wait(bar_rb_free, (j & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 5));
-          }
-          // ROW_Q: the outputs of tile j-1 read their operands from RB and were issued by this
-          // warp just before, so overwriting RB now is ordered behind them.
+          ok = mbar_wait(bar_stream_full(st), (j / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-            ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
+            ts(rb, dot + 8 * ks, strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
           commit(bar_rb_full);
           ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
           if constexpr (MODE == ROW_PREDO) {
-            const int ra_col = CF::kRA0 + b * 128;
             _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += P g_dV
-              ts(out, op_tmem(ra_col, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(j == 0 && ks == 0));
+              ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(j == 0 && ks == 0));
             _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += (P o gdS) V
-              ts(out, op_tmem(ra_col + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
-            commit(bar_ra_free(b));        // the operands in RA[b] have been consumed
+              ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
           } else {
             _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += dS g_dK
               ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(j == 0 && ks == 0));
@@ -306,18 +318,51 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     const float2 sc2 = make_float2(g.scale, g.scale);
     const float2 zero2 = make_float2(0.f, 0.f);
 
+    // ---- one-time copy of the stationary Q and dO rows from the staging buffer to tensor memory.
+    // Tile layout in shared memory: per 64-column atom, row r at r*128 bytes with its 16-byte
+    // chunks XOR-swizzled by r % 8.  Tensor-memory layout of an A operand: lane = row, one
+    // 32-bit column per pair of consecutive K elements.  This thread moves its row's half.
+    bool ok = true;
+    if (n_iter > 0) {
+      ok = mbar_wait(bar_staging_full, 0, abort_flag, t.status, wait_code(KIND, 12));
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        constexpr int kChunksPerHalf = D / 16;    // 16-byte chunks (8 halves) of this thread's half row
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {             // 0: Q, 1: dO
+          const uint32_t src = staging + x * kAtoms * kAtomBytesStat;
+          const uint32_t dst = lane_addr + (x == 0 ? CF::kQT : CF::kDOT);
+#pragma unroll
+          for (int c = 0; c < kChunksPerHalf; c += 2) {
+            uint32_t w[8];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int gc = half * kChunksPerHalf + c + u;   // chunk index within the row
+              const uint32_t addr = src + (gc >> 3) * kAtomBytesStat + row * 128 + ((((uint32_t)(gc & 7)) ^ (row & 7)) << 4);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(w[4 * u]), "=r"(w[4 * u + 1]), "=r"(w[4 * u + 2]), "=r"(w[4 * u + 3])
+                           : "r"(addr));
+            }
+            tmem_st8(dst + 4 * (half * kChunksPerHalf + c), w);
+          }
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_stat_tmem_ready);
+    }
+
     float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2 (ROW_PREDO: a_ = p * gdS)
     float2 acc_D = zero2, acc_2 = zero2, acc_A = zero2, acc_E = zero2;   // ROW_PREDO row sums
-    bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
-      const int j0 = (t_begin + it) * BN, b = it & 1;
+    const uint32_t ra = lane_addr + CF::kRA, rb = lane_addr + CF::kRB;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int j0 = (t_begin + it) * BN;
       const int first = j0 + half * 32;
       const bool masked = !(first >= vlo && first + 31 < vhi);
-      const uint32_t ra = lane_addr + CF::kRA0 + b * 128;
-      const uint32_t rb = lane_addr + CF::kRB;
 
       // ---------------- half-step 1: RA ------------------------------------------
-      ok = mbar_wait(bar_ra_full(b), (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 7));
+      ok = mbar_wait(bar_ra_full, it & 1, abort_flag, t.status, wait_code(KIND, 7));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
@@ -329,7 +374,12 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         tmem_ld16(ra + 64 + c0, g_);
         tmem_ld_wait(s_);
         tmem_ld_wait(g_);
-        uint32_t kp[8], kpg[8];
+        if (ch == 1) {
+          // every load of this region has completed: the next tile's products may overwrite it
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_ra_free);
+        }
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
           const int cc = c0 + e;
@@ -345,26 +395,10 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
             const float2 pg = __fmul2_rn(pp, __fmul2_rn(gg, sc2));     // p * gdS
             a_[ch * 8 + (e >> 1)] = pg;
             acc_2 = __fadd2_rn(acc_2, pg);
-            kp[e >> 1] = Pack<T>::pack(pp.x, pp.y);
-            kpg[e >> 1] = Pack<T>::pack(pg.x, pg.y);
           } else {
             a_[ch * 8 + (e >> 1)] = __ffma2_rn(gg, sc2, nD2);           // gdS - dot2
           }
         }
-        if constexpr (MODE == ROW_PREDO) {
-          tmem_st8(ra + half * 32 + ch * 8, kp);
-          tmem_st8(ra + 64 + half * 32 + ch * 8, kpg);
-        }
-      }
-      if constexpr (MODE == ROW_PREDO) {
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_op_full);
-      } else {
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_ra_free(b));
       }
 
       // ---------------- half-step 2: RB ------------------------------------------
@@ -380,7 +414,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         tmem_ld16(rb + 64 + c0, gp_);
         tmem_ld_wait(dp_);
         tmem_ld_wait(gp_);
-        uint32_t kds[8], kgs[8];
+        uint32_t k0[8], k1[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
           const float2 pp = p_[ch * 8 + (e >> 1)], aa = a_[ch * 8 + (e >> 1)];
@@ -390,29 +424,24 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
             acc_D = __ffma2_rn(pp, dp, acc_D);
             acc_A = __ffma2_rn(aa, dp, acc_A);
             acc_E = __ffma2_rn(pp, gp, acc_E);
+            k0[e >> 1] = Pack<T>::pack(pp.x, pp.y);      // P
+            k1[e >> 1] = Pack<T>::pack(aa.x, aa.y);      // P o gdS
           } else {
             const float2 dpd = __fadd2_rn(dp, nDv);
             const float2 ds = __fmul2_rn(pp, dpd);
             const float2 gs = __fmul2_rn(pp, __ffma2_rn(aa, dpd, __fadd2_rn(gp, nC3)));
-            kds[e >> 1] = Pack<T>::pack(ds.x, ds.y);
-            kgs[e >> 1] = Pack<T>::pack(gs.x, gs.y);
+            k0[e >> 1] = Pack<T>::pack(ds.x, ds.y);      // dS
+            k1[e >> 1] = Pack<T>::pack(gs.x, gs.y);      // g_S
           }
         }
-        if constexpr (MODE == ROW_Q) {
-          tmem_st8(rb + half * 32 + ch * 8, kds);
-          tmem_st8(rb + 64 + half * 32 + ch * 8, kgs);
-        }
+        // over columns this thread has just read (first half of its dP and gPdV ranges)
+        tmem_st8(rb + half * 32 + ch * 8, k0);
+        tmem_st8(rb + 64 + half * 32 + ch * 8, k1);
       }
-      if constexpr (MODE == ROW_Q) {
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_op_full);
-      } else {
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_rb_free);
-      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_op_full);
     }
 
     // ---------------- results ------------------------------------------------------
