@@ -98,6 +98,9 @@ int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream, int phase
   if (e0 != cudaSuccess) return fail(ATTN_ECUDA, "cudaFree(0): %s", cudaGetErrorString(e0));
   int rc = status_pointer(&t.status);
   if (rc != ATTN_OK) return rc;
+#ifdef ATTN_EXPERIMENT
+  if (const char* e = getenv("ATTN_B200_TRACE")) t.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
+#endif
   const bool use_tc = s->impl == ATTN_IMPL_TENSOR ||
                       (s->impl == ATTN_IMPL_AUTO && attn::tc_supported(s->dtype, s->D));
   cudaStream_t cs = static_cast<cudaStream_t>(stream);

@@ -134,6 +134,7 @@ struct Tensors {
   void *out_O, *out_dQ, *out_dK, *out_dV, *out_g_dO, *out_g_Q, *out_g_K, *out_g_V;
   float* out_L;
   float *Dv, *dot2, *dot3;                               // scratch, [BH, N_q] each
+  long long* trace;      // experiment builds only: per-event clock stamps of CTA 0 (else null)
   unsigned int* status;  // device status word: a kernel that gives up on a bounded
                          // wait stores a non-zero code here and returns
 };

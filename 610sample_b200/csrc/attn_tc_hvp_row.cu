@@ -26,10 +26,11 @@
 //   half-step 2 reads RB:  ROW_PREDO accumulates Dv, A, E (dot3 = A - 2 Dv dot2 + E) and
 //               writes the operands P and P o gdS over RB; ROW_Q writes dS = p (dP - Dv) and
 //               g_S = p (a (dP - Dv) + gPdV - c3), c3 = dot2 Dv + dot3, over RB.
-// Output products take their A operand from RB.  Two warps issue MMAs: warp 9 the RA
-// products, warp 10 the RB products and the outputs (in order, so RB is overwritten only
-// after the outputs that read it); one warp alone cannot issue N <= 128 instructions fast
-// enough to keep the tensor core busy.
+// Output products take their A operand from RB.  One warp issues every MMA in a fixed order
+// per tile -- RA products of the next tile (the math warps wait for those first), outputs of
+// this tile, RB products of the next tile -- so RB is overwritten only after the outputs that
+// read it.  (Two issuing warps were measured slower here: the RB work lands on top of the RA
+// products that are on the critical path.)
 // Formulas: reference csrc/flash_double_backward_v7.cu:1257-1454.
 #include "attn_launch.h"
 #include "tc_common.cuh"
@@ -39,9 +40,15 @@ namespace tc {
 
 enum RowMode { ROW_PREDO = 0, ROW_Q = 1 };
 
-constexpr int kRowMmaWarp1 = 9;     // RA products
-constexpr int kRowMmaWarp2 = 10;    // RB products and output products
-constexpr int kRowThreads = 352;
+// Experiment builds record clock stamps of CTA 0: slot = tile * 16 + event.
+#ifdef ATTN_EXPERIMENT
+#define ROW_TRACE(tile_, ev_) do { if (t.trace != nullptr && blockIdx.x == 0 && (tile_) < 64) t.trace[(tile_) * 16 + (ev_)] = clock64(); } while (0)
+#else
+#define ROW_TRACE(tile_, ev_) do { } while (0)
+#endif
+
+constexpr int kRowMmaWarp = 9;
+constexpr int kRowThreads = 320;
 
 constexpr int kRowStages = 3;
 
@@ -140,7 +147,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     mbar_init(bar_stat_tmem_ready, kMathWarps);
     for (int s = 0; s < kRowStages; ++s) {
       mbar_init(bar_stream_full(s), 1);
-      mbar_init(bar_stream_empty(s), 2);      // one commit per MMA warp
+      mbar_init(bar_stream_empty(s), 1);
     }
     mbar_init(bar_ra_full, 1);
     mbar_init(bar_ra_free, kMathWarps);
@@ -153,7 +160,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (warp == kRowMmaWarp1) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+  if (warp == kRowMmaWarp) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -204,7 +211,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   // =========================================================================
   // MMA issuers (converged warps, one elected lane issues)
   // =========================================================================
-  else if (warp == kRowMmaWarp1 || warp == kRowMmaWarp2) {
+  else if (warp == kRowMmaWarp) {
     if (n_iter > 0) {
       bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
       if (ok) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 11));
@@ -235,55 +242,71 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       const uint32_t ra = tmem_base + CF::kRA, rb = tmem_base + CF::kRB;
       const uint32_t qt = tmem_base + CF::kQT, dot = tmem_base + CF::kDOT;
 
-      if (warp == kRowMmaWarp1) {
-        // ---- RA products: [S | Q g_dK^T] = Q [K; g_dK]^T (Q from tensor memory), gdS += g_dQ K^T ----
-        for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j % kRowStages;
-          const uint32_t stage = strm_base + st * CF::kStageBytes;
-          ok = mbar_wait(bar_stream_full(st), (j / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
-          if (ok) ok = mbar_wait(bar_ra_free, (j & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 4));
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-            ts(ra, qt + 8 * ks, strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-            ss(ra + 64, gq_desc(ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
-          commit(bar_ra_full);
-          commit(bar_stream_empty(st));
+      auto issue_ra = [&](uint32_t stage) {
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          ts(ra, qt + 8 * ks, strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          ss(ra + 64, gq_desc(ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+      };
+      auto issue_rb = [&](uint32_t stage) {
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          ts(rb, dot + 8 * ks, strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
+      };
+      auto issue_out = [&](uint32_t stage, bool first) {
+        if constexpr (MODE == ROW_PREDO) {
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += P g_dV
+            ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += (P o gdS) V
+            ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
+        } else {
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += dS g_dK
+            ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += g_S K
+            ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
         }
-      } else {
-        // ---- RB products [dP | gPdV] = dO [V; g_dV]^T (dO from tensor memory) and the outputs.
-        // The outputs of tile j read their operands from RB and are issued by this warp before
-        // the RB products of tile j+1, so RB is overwritten only after they have read it.
-        for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j % kRowStages;
-          const uint32_t stage = strm_base + st * CF::kStageBytes;
-          ok = mbar_wait(bar_stream_full(st), (j / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
+      };
+
+      {
+        {
+          // tile 0: both regions
+          ok = ok && mbar_wait(bar_stream_full(0), 0, abort_flag, t.status, wait_code(KIND, 3));
           ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-            ts(rb, dot + 8 * ks, strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
-          commit(bar_rb_full);
-          ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
-          if constexpr (MODE == ROW_PREDO) {
-            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += P g_dV
-              ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(j == 0 && ks == 0));
-            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += (P o gdS) V
-              ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
-          } else {
-            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += dS g_dK
-              ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(j == 0 && ks == 0));
-            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += g_S K
-              ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_ra(strm_base); commit(bar_ra_full);
+            issue_rb(strm_base); commit(bar_rb_full);
           }
-          commit(bar_stream_empty(st));
+          for (int j = 0; j < n_iter && ok; ++j) {
+            const int st = j % kRowStages, nst = (j + 1) % kRowStages;
+            const bool more = j + 1 < n_iter;
+            if (more) {
+              // RA of tile j has been read: next tile's RA products first, the math warps wait for them
+              ok = mbar_wait(bar_stream_full(nst), ((j + 1) / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
+              if (ok) ok = mbar_wait(bar_ra_free, j & 1, abort_flag, t.status, wait_code(KIND, 4));
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+              tc_fence_after_sync();
+              if (lane == 0) ROW_TRACE(j + 1, 0);
+              issue_ra(strm_base + nst * CF::kStageBytes);
+              commit(bar_ra_full);
+              if (lane == 0) ROW_TRACE(j + 1, 1);
+            }
+            ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (lane == 0) ROW_TRACE(j, 4);
+            issue_out(strm_base + st * CF::kStageBytes, j == 0);
+            commit(bar_stream_empty(st));
+            if (lane == 0) ROW_TRACE(j, 5);
+            if (more) {
+              issue_rb(strm_base + nst * CF::kStageBytes);   // after the outputs that read RB (in order)
+              commit(bar_rb_full);
+              if (lane == 0) ROW_TRACE(j + 1, 3);
+            }
+          }
+          if (ok) commit(bar_acc_done);
         }
-        if (ok) commit(bar_acc_done);
       }
     }
   }
@@ -366,30 +389,34 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 0) ROW_TRACE(it, 6);
+      // Read this thread's 2 x 32 columns of RA in one go and release the region before the
+      // arithmetic: the next tile's RA products are what the math warps wait for next.
+      uint32_t s_[2][16], g_[2][16];
+      tmem_ld16(ra + half * 32, s_[0]);
+      tmem_ld16(ra + half * 32 + 16, s_[1]);
+      tmem_ld16(ra + 64 + half * 32, g_[0]);
+      tmem_ld16(ra + 64 + half * 32 + 16, g_[1]);
+      tmem_ld_wait(s_[0]);
+      tmem_ld_wait(s_[1]);
+      tmem_ld_wait(g_[0]);
+      tmem_ld_wait(g_[1]);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ra_free);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const int c0 = half * 32 + ch * 16;
-        uint32_t s_[16], g_[16];
-        tmem_ld16(ra + c0, s_);
-        tmem_ld16(ra + 64 + c0, g_);
-        tmem_ld_wait(s_);
-        tmem_ld_wait(g_);
-        if (ch == 1) {
-          // every load of this region has completed: the next tile's products may overwrite it
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_ra_free);
-        }
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
           const int cc = c0 + e;
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(s_[e]), __uint_as_float(s_[e + 1])), sl2, nL2);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(s_[ch][e]), __uint_as_float(s_[ch][e + 1])), sl2, nL2);
           float2 pp = make_float2(ex2(x.x), ex2(x.y));
           if (masked) {
             pp.x = ((uint32_t)(j0 + cc - vlo) < vspan) ? pp.x : 0.f;
             pp.y = ((uint32_t)(j0 + cc + 1 - vlo) < vspan) ? pp.y : 0.f;
           }
-          const float2 gg = make_float2(__uint_as_float(g_[e]), __uint_as_float(g_[e + 1]));
+          const float2 gg = make_float2(__uint_as_float(g_[ch][e]), __uint_as_float(g_[ch][e + 1]));
           p_[ch * 8 + (e >> 1)] = pp;
           if constexpr (MODE == ROW_PREDO) {
             const float2 pg = __fmul2_rn(pp, __fmul2_rn(gg, sc2));     // p * gdS
@@ -402,10 +429,12 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       }
 
       // ---------------- half-step 2: RB ------------------------------------------
+      if (threadIdx.x == 0) ROW_TRACE(it, 7);
       ok = mbar_wait(bar_rb_full, it & 1, abort_flag, t.status, wait_code(KIND, 8));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 0) ROW_TRACE(it, 8);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const int c0 = half * 32 + ch * 16;
@@ -442,6 +471,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_op_full);
+      if (threadIdx.x == 0) ROW_TRACE(it, 9);
     }
 
     // ---------------- results ------------------------------------------------------
@@ -508,7 +538,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kRowMmaWarp1) {
+  if (warp == kRowMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
