@@ -247,8 +247,15 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   // MMA issuer
   // =========================================================================
   else if (warp == kMmaWarp) {
-    if (lane == 0 && n_iter > 0) {
+    // the whole warp runs this loop converged; one elected lane issues (keeps the descriptors in
+    // uniform registers: a single diverged lane issues about 1.5x slower)
+    if (n_iter > 0) {
       bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
+      ok = __all_sync(0xffffffffu, ok);
+      auto mma_ss_e = [&](uint32_t d, uint64_t a_, uint64_t b_, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ss(d, a_, b_, idesc, acc);
+      };
+      auto commit_e = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
       // Descriptor of (base + byte offset) == descriptor of base + (offset >> 4): shared-memory
       // addresses stay below 2^18, so the 14-bit start-address field never carries.
       const uint64_t d_stat = smem_desc_sw128(stat_base, 16, 1024);
@@ -271,28 +278,28 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         const uint32_t c0 = tmem_base + TR::kScoreCol0 + sb * TR::kNScore * 64;
         constexpr int KS = D / 16;
         if constexpr (KIND == FWD_LSE || KIND == FWD_OUT) {
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc64, ks > 0);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc64, ks > 0);
         } else if constexpr (KIND == BWD_ROW || KIND == BWD_COL) {
           // slot 0: S (or S^T), slot 1: dP (or dP^T)
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc64, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(c0 + 64, stat_desc(1, ks), strm_desc_k(stage, 1, ks), kIdesc64, ks > 0);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc64, ks > 0);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(c0 + 64, stat_desc(1, ks), strm_desc_k(stage, 1, ks), kIdesc64, ks > 0);
         } else if constexpr (KIND == HVP_PRE || KIND == HVP_ROW) {
           // slots: 0 S | 1 gdS | 2 dP | 3 gPdV.  stat: 0 Q, 1 dO, 2 g_dQ.  stream: 0 K, 1 g_dK, 2 V, 3 g_dV
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S | Q g_dK^T] = Q [K ; g_dK]^T
-            mma_ss(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
+            mma_ss_e(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [dP | gPdV] = dO [V ; g_dV]^T
-            mma_ss(c0 + 128, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
+            mma_ss_e(c0 + 128, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS += g_dQ K^T
-            mma_ss(c0 + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+            mma_ss_e(c0 + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
         } else {   // HVP_COL.  stat: 0 K, 1 V, 2 g_dK, 3 g_dV.  stream: 0 Q, 1 g_dQ, 2 dO
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S^T | K g_dQ^T] = K [Q ; g_dQ]^T
-            mma_ss(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
+            mma_ss_e(c0, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS^T += g_dK Q^T
-            mma_ss(c0 + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+            mma_ss_e(c0 + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // dP^T = V dO^T
-            mma_ss(c0 + 128, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
+            mma_ss_e(c0 + 128, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gPdV^T = g_dV dO^T
-            mma_ss(c0 + 192, stat_desc(3, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
+            mma_ss_e(c0 + 192, stat_desc(3, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
         }
       };
       // output products of one tile; `first` clears the accumulators
@@ -301,44 +308,48 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         constexpr int KS = BN / 16;
         (void)o1;
         if constexpr (KIND == FWD_OUT) {          // O += P V
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
         } else if constexpr (KIND == BWD_ROW) {   // dQ += dS K
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o0, op_desc(0, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o0, op_desc(0, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
         } else if constexpr (KIND == BWD_COL) {   // dV += P^T dO ; dK += dS^T Q
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o1, op_desc(1, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o1, op_desc(1, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
         } else if constexpr (KIND == HVP_ROW) {   // ops: 0 dS, 1 g_S, 2 P, 3 g_dp
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));  // dS g_dK
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o0, op_desc(1, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);                    // g_S K
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o1, op_desc(2, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(first && ks == 0));  // P g_dV
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o1, op_desc(3, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);                    // g_dp V
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));  // dS g_dK
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o0, op_desc(1, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);                    // g_S K
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o1, op_desc(2, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(first && ks == 0));  // P g_dV
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o1, op_desc(3, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);                    // g_dp V
         } else if constexpr (KIND == HVP_COL) {   // ops: 0 dS^T, 1 g_S^T, 2 g_dp^T
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));  // dS^T g_dQ
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o0, op_desc(1, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);                    // g_S^T Q
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss(o1, op_desc(2, ks), strm_desc_mn(stage, 2, ks), kIdescOut, !(first && ks == 0));  // g_dp^T dO
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o0, op_desc(0, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));  // dS^T g_dQ
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o0, op_desc(1, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);                    // g_S^T Q
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks) mma_ss_e(o1, op_desc(2, ks), strm_desc_mn(stage, 2, ks), kIdescOut, !(first && ks == 0));  // g_dp^T dO
         }
       };
       auto do_out = [&](int k) -> bool {
-        if (!mbar_wait(bar_opnd_full, k & 1, abort_flag, t.status, wait_code(KIND, 5))) return false;
+        bool okw = mbar_wait(bar_opnd_full, k & 1, abort_flag, t.status, wait_code(KIND, 5));
+        okw = __all_sync(0xffffffffu, okw);
+        if (!okw) return false;
         tc_fence_after_sync();
         const int st = k % TR::kStages;
         if (!dbg_skip_mma) issue_outs(strm_base + st * TR::kStageBytes, k == 0);
-        mma_commit(bar_opnd_free);
-        mma_commit(bar_stream_empty(st));
+        commit_e(bar_opnd_free);
+        commit_e(bar_stream_empty(st));
         return true;
       };
 
       for (int it = 0; it < n_iter && ok; ++it) {
         const int st = it % TR::kStages, sb = it % TR::kScoreBufs;
         ok = mbar_wait(bar_stream_full(st), (it / TR::kStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         ok = mbar_wait(bar_score_free(sb), ((it / TR::kScoreBufs) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 4));
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
         if (!dbg_skip_mma) issue_scores(strm_base + st * TR::kStageBytes, sb);
-        mma_commit(bar_score_full(sb));
+        commit_e(bar_score_full(sb));
         if constexpr (TR::kReduce) {
-          mma_commit(bar_stream_empty(st));
+          commit_e(bar_stream_empty(st));
         } else if constexpr (TR::kLookahead) {
           if (it > 0) ok = do_out(it - 1);
         } else {
@@ -347,7 +358,7 @@ attn_tc_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       }
       if constexpr (!TR::kReduce) {
         if constexpr (TR::kLookahead) { if (ok) ok = do_out(n_iter - 1); }
-        if (ok) mma_commit(bar_acc_done);
+        if (ok) commit_e(bar_acc_done);
       }
     }
   }
