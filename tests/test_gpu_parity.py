@@ -164,3 +164,41 @@ def test_linearity_in_tangents_at_headline_size():
     O1, _ = tcapi.forward(g["Q"], g["K"], torch.ones_like(g["V"]), 4096, 0)
     assert float((O1.float() - 1).abs().max()) < 1e-2
     assert capi.device_status() == 0
+
+
+def test_noncausal_config_full_size_heads_against_fp64_oracle():
+    """BASELINE configs[1]: bf16, no mask, N=2048, D=64, Q/K/V scaled by 0.5, fp32 LSE.  All 64
+    (batch, head) slices run on the GPU; two of them are checked against the fp64 oracle."""
+    B, H, N, D = 4, 16, 2048, 64
+    inp = orc.make_inputs(B, H, N, N, D, seed=0, dtype=torch.bfloat16, qk_scale=0.5, v_scale=0.5)
+    got = run_all(inp, N, 0, 1, 0)
+    for (b, h) in ((0, 0), (3, 11)):
+        one = {n: t[b:b + 1, h:h + 1] for n, t in inp.items()}
+        ref = orc.closed_form_all(*(one[n] for n in orc.INPUT_NAMES), window_size=N, chunk_id=0, mask_mode=1)
+        sub = {n: t[b:b + 1, h:h + 1] for n, t in got.items()}
+        check_half(sub, ref, torch.bfloat16, f"config2 head {b},{h}")
+
+
+def test_long_context_peaked_softmax_config():
+    """BASELINE configs[3] shape (N=16384, D=128, causal, Q and K scaled by 2) on two heads:
+    tensor-core kernels against the fp32 SIMT kernels on the same bf16 inputs, and exact
+    linearity of the HVP in the tangents."""
+    N, D = 16384, 128
+    inp = orc.make_inputs(1, 2, N, N, D, seed=0, dtype=torch.bfloat16, qk_scale=2.0)
+    a = run_all(inp, N, 0, 0, 2)
+    b = run_all(inp, N, 0, 0, 1)
+    for n in orc.OUTPUT_NAMES:
+        assert torch.isfinite(a[n]).all(), n
+        if n == "L":
+            assert (a[n] - b[n]).abs().max() < 2e-4 * float(b[n].abs().max())
+        else:
+            tol = HALF_RTOL[torch.bfloat16] * max(1.0, float(b[n].abs().max()))
+            assert float((a[n] - b[n]).abs().max()) <= tol, n
+    g = {n: t.to(DEV) for n, t in inp.items()}
+    O, L = tcapi.forward(g["Q"], g["K"], g["V"], N, 0)
+    base = tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, N, 0)
+    half = tcapi.double_backward(0.5 * g["g_dQ"], 0.5 * g["g_dK"], 0.5 * g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, N, 0)
+    torch.cuda.synchronize()
+    for x, y in zip(base, half):
+        assert torch.equal(0.5 * x.float(), y.float())
+    assert capi.device_status() == 0
