@@ -65,6 +65,8 @@ int check_shape(const attn_shape_t* s) {
   return ATTN_OK;
 }
 
+bool shape_is_empty(const attn_shape_t* s) { return s->B == 0 || s->H == 0 || s->N_q == 0 || s->N_kv == 0; }
+
 attn::Geometry make_geometry(const attn_shape_t* s) {
   attn::Geometry g;
   g.BH = s->B * s->H;
@@ -87,10 +89,40 @@ attn::Geometry make_geometry(const attn_shape_t* s) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Empty problems (N_q == 0 or N_kv == 0) launch no attention kernel: whatever outputs exist
+// are all-masked, i.e. zero, and L is -inf.
+__global__ void fill_f32_kernel(float* p, size_t n, float v) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
+}
+
+cudaError_t fill_zero(void* p, size_t elems, int dtype, cudaStream_t s) {
+  if (p == nullptr || elems == 0) return cudaSuccess;
+  return cudaMemsetAsync(p, 0, elems * (dtype == ATTN_F32 ? 4 : 2), s);
+}
+
+int run_empty(int op, const attn_shape_t* s, attn::Tensors& t, cudaStream_t cs) {
+  const size_t nq = (size_t)s->B * s->H * s->N_q * s->D, nkv = (size_t)s->B * s->H * s->N_kv * s->D;
+  cudaError_t e = cudaSuccess;
+  void* q_outs[] = {t.out_O, t.out_dQ, t.out_g_dO, t.out_g_Q};
+  void* kv_outs[] = {t.out_dK, t.out_dV, t.out_g_K, t.out_g_V};
+  for (void* p : q_outs) if (e == cudaSuccess) e = fill_zero(p, nq, s->dtype, cs);
+  for (void* p : kv_outs) if (e == cudaSuccess) e = fill_zero(p, nkv, s->dtype, cs);
+  const size_t rows = (size_t)s->B * s->H * s->N_q;
+  if (e == cudaSuccess && op == attn::OP_FORWARD && t.out_L != nullptr && rows > 0) {
+    fill_f32_kernel<<<(unsigned)((rows + 255) / 256 > 1024 ? 1024 : (rows + 255) / 256), 256, 0, cs>>>(t.out_L, rows, -INFINITY);
+    e = cudaGetLastError();
+    tl_launches = 1;
+  }
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "empty-problem fill failed: %s", cudaGetErrorString(e));
+  tl_error[0] = 0;
+  return ATTN_OK;
+}
+
 int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream, int phases = attn::HVP_PHASE_ALL) {
   const attn::Geometry g = make_geometry(s);
   tl_launches = 0;
   if (g.BH == 0 || (g.N_q == 0 && g.N_kv == 0)) return ATTN_OK;
+  if (g.N_q == 0 || g.N_kv == 0) return run_empty(op, s, t, static_cast<cudaStream_t>(stream));
   // Bind the device's primary context to this host thread.  Tensor-map encoding is a
   // driver call and fails with "invalid context" on a thread that has made no runtime
   // call yet (e.g. a freshly started autograd worker thread).
@@ -118,10 +150,12 @@ int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream, int phase
   return ATTN_OK;
 }
 
-#define REQUIRE_PTR(p)                                                       \
-  do {                                                                       \
-    if ((p) == nullptr) return fail(ATTN_EINVAL, #p " is null");             \
-    if (!aligned16(p)) return fail(ATTN_EINVAL, #p " is not 16-byte aligned"); \
+// A tensor without elements (B, H, N or the other side's N is 0) may be passed as null.
+#define REQUIRE_PTR(p)                                                                        \
+  do {                                                                                        \
+    if ((p) == nullptr) {                                                                     \
+      if (!shape_is_empty(shape)) return fail(ATTN_EINVAL, #p " is null");                    \
+    } else if (!aligned16(p)) return fail(ATTN_EINVAL, #p " is not 16-byte aligned");          \
   } while (0)
 
 }  // namespace
@@ -133,7 +167,7 @@ int attn_b200_forward(const attn_shape_t* shape, const void* Q, const void* K, c
   int rc = check_shape(shape);
   if (rc != ATTN_OK) return rc;
   REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
-  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
+  if (L == nullptr && !shape_is_empty(shape)) return fail(ATTN_EINVAL, "L is null");
   attn::Tensors t;
   memset(&t, 0, sizeof(t));
   t.Q = Q; t.K = K; t.V = V; t.out_O = O; t.out_L = L;
@@ -152,8 +186,8 @@ int attn_b200_backward(const attn_shape_t* shape, const void* dO, const void* Q,
   if (rc != ATTN_OK) return rc;
   REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
   REQUIRE_PTR(dQ); REQUIRE_PTR(dK); REQUIRE_PTR(dV);
-  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
-  if (scratch == nullptr) return fail(ATTN_EINVAL, "scratch is null");
+  if (L == nullptr && !shape_is_empty(shape)) return fail(ATTN_EINVAL, "L is null");
+  if (scratch == nullptr && !shape_is_empty(shape)) return fail(ATTN_EINVAL, "scratch is null");
   attn::Tensors t;
   memset(&t, 0, sizeof(t));
   t.dO = dO; t.Q = Q; t.K = K; t.V = V; t.O = O; t.L = L;
@@ -185,8 +219,8 @@ int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ
   REQUIRE_PTR(g_dQ); REQUIRE_PTR(g_dK); REQUIRE_PTR(g_dV);
   REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
   REQUIRE_PTR(g_dO); REQUIRE_PTR(g_Q); REQUIRE_PTR(g_K); REQUIRE_PTR(g_V);
-  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
-  if (scratch == nullptr) return fail(ATTN_EINVAL, "scratch is null");
+  if (L == nullptr && !shape_is_empty(shape)) return fail(ATTN_EINVAL, "L is null");
+  if (scratch == nullptr && !shape_is_empty(shape)) return fail(ATTN_EINVAL, "scratch is null");
   attn::Tensors t;
   memset(&t, 0, sizeof(t));
   t.g_dQ = g_dQ; t.g_dK = g_dK; t.g_dV = g_dV;
@@ -240,7 +274,7 @@ int attn_b200_double_backward_static(const attn_shape_t* shape, const void* g_dQ
   REQUIRE_PTR(g_dQ); REQUIRE_PTR(g_dK); REQUIRE_PTR(g_dV);
   REQUIRE_PTR(dO); REQUIRE_PTR(Q); REQUIRE_PTR(K); REQUIRE_PTR(V); REQUIRE_PTR(O);
   REQUIRE_PTR(g_dO); REQUIRE_PTR(g_Q); REQUIRE_PTR(g_K); REQUIRE_PTR(g_V);
-  if (L == nullptr) return fail(ATTN_EINVAL, "L is null");
+  if (L == nullptr && !shape_is_empty(shape)) return fail(ATTN_EINVAL, "L is null");
   const long long rows = (long long)shape->B * shape->H * shape->N_q;
   if (rows > (long long)ATTN_B200_STATIC_SCRATCH_ROWS)
     return fail(ATTN_ETOOLARGE,
@@ -250,6 +284,12 @@ int attn_b200_double_backward_static(const attn_shape_t* shape, const void* g_dQ
   tl_launches = 0;
   const attn::Geometry g = make_geometry(shape);
   if (g.BH == 0 || (g.N_q == 0 && g.N_kv == 0)) return ATTN_OK;
+  if (g.N_q == 0 || g.N_kv == 0) {
+    attn::Tensors te;
+    memset(&te, 0, sizeof(te));
+    te.out_g_dO = g_dO; te.out_g_Q = g_Q; te.out_g_K = g_K; te.out_g_V = g_V;
+    return run_empty(attn::OP_DOUBLE_BACKWARD, shape, te, static_cast<cudaStream_t>(stream));
+  }
 
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

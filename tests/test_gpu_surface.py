@@ -158,3 +158,27 @@ def test_multi_stream_and_device_guard(mods):
         O1, L1 = ac.v7_forward(g["Q"], g["K"], g["V"], 256, 0)
     s.synchronize()
     assert torch.equal(O0, O1) and torch.equal(L0, L1)
+
+
+def test_empty_inputs(mods):
+    """No keys: every row is fully masked (O = 0, L = -inf, zero gradients).  No queries: the
+    key-side gradients are zero.  No kernel of the attention families is launched."""
+    ac, _ = mods
+    q = torch.randn(2, 3, 40, 64, device=DEV).to(torch.bfloat16)
+    k0 = torch.empty(2, 3, 0, 64, device=DEV, dtype=torch.bfloat16)
+    O, L = ac.v7_forward(q, k0, k0, 16, 0)
+    assert O.shape == q.shape and float(O.float().abs().max()) == 0.0
+    assert bool(torch.isinf(L).all()) and bool((L < 0).all())
+    dQ, dK, dV = ac.v7_backward(torch.ones_like(q), q, k0, k0, O, L, 16, 0)
+    assert float(dQ.float().abs().max()) == 0.0 and dK.numel() == 0 and dV.numel() == 0
+    g = ac.v7_double_backward(q, k0, k0, q, q, k0, k0, O, L, 16, 0)
+    assert float(g[0].float().abs().max()) == 0.0 and float(g[1].float().abs().max()) == 0.0
+    q0 = torch.empty(2, 3, 0, 64, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(2, 3, 50, 64, device=DEV).to(torch.bfloat16)
+    O0, L0 = ac.v7_forward(q0, k, k, 16, 0)
+    assert O0.numel() == 0 and L0.numel() == 0
+    dQ, dK, dV = ac.v7_backward(q0, q0, k, k, O0, L0, 16, 0)
+    assert dQ.numel() == 0 and float(dK.float().abs().max()) == 0.0 and float(dV.float().abs().max()) == 0.0
+    none = torch.empty(0, 3, 8, 64, device=DEV, dtype=torch.bfloat16)
+    O1, L1 = ac.v7_forward(none, none, none, 16, 0)
+    assert O1.numel() == 0 and ac.last_launch_count() == 0
