@@ -833,8 +833,8 @@ bool encode_all_maps(TmaMaps* maps, const Geometry& g, const Tensors& t, int is_
   return true;
 }
 
-cudaError_t launch_hvp_main(bool col, int D, int is_bf16, const TmaMaps& maps, const Geometry& g,
-                            const Tensors& t, cudaStream_t s);
+cudaError_t launch_hvp_col(int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
+                           cudaStream_t s);
 cudaError_t launch_hvp_row(int mode, int D, int is_bf16, const TmaMaps& maps, const Geometry& g,
                            const Tensors& t, cudaStream_t s);
 
@@ -880,23 +880,9 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
     if (e == cudaSuccess) e = launch_kind<BWD_COL, D, T>(maps, g, t, s);
     *n = 3;
   } else {
-    // debug 8 / 16 select earlier generations of the row-side kernels (experiment builds)
-    if (phases & HVP_PHASE_PRE) {
-      e = (g.debug & 24) ? launch_kind<HVP_PRE, D, T>(maps, g, t, s)
-                         : launch_hvp_row(0, D, Pack<T>::kIsBf16, maps, g, t, s);   // scalars + g_dO
-      ++*n;
-    }
-    if (e == cudaSuccess && (phases & HVP_PHASE_ROW)) {
-      e = (g.debug & 8) ? launch_kind<HVP_ROW, D, T>(maps, g, t, s)
-          : (g.debug & 16) ? launch_hvp_main(false, D, Pack<T>::kIsBf16, maps, g, t, s)
-                           : launch_hvp_row(1, D, Pack<T>::kIsBf16, maps, g, t, s);  // g_Q
-      ++*n;
-    }
-    if (e == cudaSuccess && (phases & HVP_PHASE_COL)) {
-      e = (g.debug & 8) ? launch_kind<HVP_COL, D, T>(maps, g, t, s)
-                        : launch_hvp_main(true, D, Pack<T>::kIsBf16, maps, g, t, s);
-      ++*n;
-    }
+    if (phases & HVP_PHASE_PRE) { e = launch_hvp_row(0, D, Pack<T>::kIsBf16, maps, g, t, s); ++*n; }   // scalars + g_dO
+    if (e == cudaSuccess && (phases & HVP_PHASE_ROW)) { e = launch_hvp_row(1, D, Pack<T>::kIsBf16, maps, g, t, s); ++*n; }  // g_Q
+    if (e == cudaSuccess && (phases & HVP_PHASE_COL)) { e = launch_hvp_col(D, Pack<T>::kIsBf16, maps, g, t, s); ++*n; }     // g_K, g_V
   }
   return e;
 }

@@ -1,0 +1,463 @@
+// Column side of the double backward (Hessian-vector product) on sm_100a: g_K and g_V,
+// given the per-row scalars Dv, dot2, dot3 of the row-side pre-pass.
+//
+// A CTA owns 128 key rows (stationary K, V, g_dK, g_dV in shared memory) and streams 64-row
+// query tiles (Q, g_dQ, dO; two TMA stages).  Scores are computed TRANSPOSED (keys on the
+// tensor-memory lanes), so the operand roles are those of the row kernels.
+// Tensor memory (512 columns):
+//     RA [  0,128) = [ S^T | gdS^T ] = K [Q; g_dQ]^T (one N = 128 product), gdS^T += g_dK Q^T
+//     RB [128,256) = [ dP^T | gPdV^T ] = V dO^T, g_dV dO^T
+//     OUT0 [256,256+D) = g_K += dS^T g_dQ + g_S^T Q        OUT1 [256+D,256+2D) = g_V += g_dp^T dO
+// Per tile the math warps run two half-steps.  Half-step 1 reads RA, releases it at once and
+// keeps p = exp(S - L) and a = gdS - dot2 in registers.  Half-step 2 reads RB and writes the
+// half-precision operands dS = p (dP - Dv), g_dp = p a and g_S = p (a (dP - Dv) + gPdV - c3),
+// c3 = dot2 Dv + dot3, over the RB columns the thread has just read; the output products take
+// them from there (A operand in tensor memory), so no operand tile goes through shared memory
+// and the two column halves of a row never race.  The per-query scalars (L, Dv, dot2, c3) of the
+// streamed tile are staged in shared memory by the math warps themselves.
+// One warp issues every MMA in a fixed order per tile: RA products of the next tile (the math
+// warps wait for those first), output products of this tile, RB products of the next tile, so
+// RB is overwritten only after the outputs that read it.
+// Formulas: reference csrc/flash_double_backward_v7.cu:1583-1675.
+#include "attn_launch.h"
+#include "tc_common.cuh"
+
+namespace attn {
+namespace tc {
+
+constexpr int kColMmaWarp = 9;
+constexpr int kColThreads = 320;
+
+struct ColControl {
+  uint64_t stat_full;
+  uint64_t stream_full[2];
+  uint64_t stream_empty[2];
+  uint64_t ra_full, ra_free;
+  uint64_t rb_full;
+  uint64_t op_full;
+  uint64_t acc_done;
+  uint64_t stats_ready[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+template <int D>
+struct ColCfg {
+  static constexpr int kAtoms = D / 64;
+  static constexpr int kNStat = 4;      // K, V, g_dK, g_dV
+  static constexpr int kNStream = 3;    // Q, g_dQ (back to back), dO
+  static constexpr uint32_t kStatBytes = kNStat * kAtoms * kAtomBytesStat;
+  static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
+  static constexpr uint32_t kAuxBytes = 256 + 2048;   // control block + [2][4][64] per-query scalars
+  static constexpr uint32_t kContentBytes = kStatBytes + 2 * kStageBytes + kAuxBytes;
+  static constexpr uint32_t kMaxSmem = 232448;
+  static_assert(kContentBytes + 768 <= kMaxSmem, "shared memory over-subscribed");
+  static constexpr uint32_t kSmemBytes = (kContentBytes + 1024 <= kMaxSmem) ? kContentBytes + 1024 : kMaxSmem;
+  static constexpr int kRA = 0, kRB = 128, kOut0 = 256, kOut1 = 256 + D;
+  static_assert(kOut1 + D <= kTmemCols, "tensor memory over-subscribed");
+  __host__ __device__ static constexpr uint32_t stream_off(int slot, int atom) {
+    if (slot < 2) return (uint32_t)atom * 2u * kAtomBytesStrm + (uint32_t)slot * kAtomBytesStrm;
+    return 2u * kAtoms * kAtomBytesStrm + (uint32_t)atom * kAtomBytesStrm;
+  }
+  __host__ __device__ static constexpr uint32_t stream_atom_stride(int slot) {
+    return slot < 2 ? 2u * kAtomBytesStrm : kAtomBytesStrm;
+  }
+  __host__ __device__ static constexpr int stat_tensor(int slot) {
+    return slot == 0 ? T_K : slot == 1 ? T_V : slot == 2 ? T_gK : T_gV;
+  }
+  __host__ __device__ static constexpr int stream_tensor(int slot) { return slot == 0 ? T_Q : slot == 1 ? T_gQ : T_dO; }
+};
+
+template <int D, typename T>
+__global__ void __launch_bounds__(kColThreads, 1)
+hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors t) {
+  using CF = ColCfg<D>;
+  constexpr int KIND = HVP_COL;
+  constexpr int kAtoms = CF::kAtoms;
+  constexpr uint32_t kIdesc64 = make_idesc(BM, 64, Pack<T>::kIsBf16, 0, 0);
+  constexpr uint32_t kIdesc128 = make_idesc(BM, 128, Pack<T>::kIsBf16, 0, 0);
+  constexpr uint32_t kIdescOut = make_idesc(BM, D, Pack<T>::kIsBf16, 0, 1);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  {
+    uint32_t dyn_size;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    if (smem_base - smem_u32(smem_raw) + CF::kContentBytes > dyn_size) {   // uniform over the CTA
+      if (threadIdx.x == 0 && t.status != nullptr) atomicCAS(t.status, 0u, wait_code(KIND, 15));
+      return;
+    }
+  }
+  const uint32_t stat_base = smem_base;
+  const uint32_t strm_base = stat_base + CF::kStatBytes;
+  const uint32_t aux_off = CF::kStatBytes + 2 * CF::kStageBytes;
+  ColControl* ctl = reinterpret_cast<ColControl*>(smem_gen + aux_off);
+  float* col_stats = reinterpret_cast<float*>(smem_gen + aux_off + 256);   // [2][4][64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles = (g.N_kv + BM - 1) / BM;
+  const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
+  const int tile = g.tile_major ? (int)(blockIdx.x / g.BH) : (int)(blockIdx.x - bh * tiles);   // early key tiles are the heavy ones
+  const int r0 = tile * BM;
+
+  int lo, hi;
+  query_range_for_keys(g, r0, r0 + BM, lo, hi);
+  const int t_begin = lo / BN;
+  const int n_iter = (hi > lo) ? ((hi + BN - 1) / BN - t_begin) : 0;
+
+  const uint32_t bar_stat_full = smem_u32(&ctl->stat_full);
+  const uint32_t bar_ra_full = smem_u32(&ctl->ra_full), bar_ra_free = smem_u32(&ctl->ra_free);
+  const uint32_t bar_rb_full = smem_u32(&ctl->rb_full);
+  const uint32_t bar_op_full = smem_u32(&ctl->op_full), bar_acc_done = smem_u32(&ctl->acc_done);
+  auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
+  auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_stat_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_stream_full(s), 1);
+      mbar_init(bar_stream_empty(s), 1);
+      mbar_init(smem_u32(&ctl->stats_ready[s]), kMathWarps);
+    }
+    mbar_init(bar_ra_full, 1);
+    mbar_init(bar_ra_free, kMathWarps);
+    mbar_init(bar_rb_full, 1);
+    mbar_init(bar_op_full, kMathWarps);
+    mbar_init(bar_acc_done, 1);
+    ctl->abort_flag = 0u;
+    ctl->tmem_base = 0u;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (warp == kColMmaWarp) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  // =========================================================================
+  // TMA producer
+  // =========================================================================
+  if (warp == kProducerWarp) {
+    if (lane == 0 && n_iter > 0) {
+      for (int i = 0; i < T_COUNT; ++i) tma_prefetch_desc(&maps.m[i]);
+      mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
+#pragma unroll
+      for (int s = 0; s < CF::kNStat; ++s)
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            tma_load_3d(stat_base + (s * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm,
+                        &maps.m[CF::stat_tensor(s)], a * 64, r0 + h * 64, bh, bar_stat_full);
+      bool ok = true;
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(bar_stream_empty(st), ((it >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
+        const uint32_t stage = strm_base + st * CF::kStageBytes;
+#pragma unroll
+        for (int s = 0; s < CF::kNStream; ++s)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(stage + CF::stream_off(s, a), &maps.m[CF::stream_tensor(s)], a * 64,
+                        (t_begin + it) * BN, bh, bar_stream_full(st));
+      }
+      if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+      }
+    }
+  }
+  // =========================================================================
+  // MMA issuer (converged warp, one elected lane issues)
+  // =========================================================================
+  else if (warp == kColMmaWarp) {
+    if (n_iter > 0) {
+      bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
+      ok = __all_sync(0xffffffffu, ok);
+      const uint64_t d_stat = smem_desc_sw128(stat_base, 16, 1024);
+      auto stat_desc = [&](int slot, int ks) {   // K-major A from shared memory
+        return d_stat + (uint64_t)(((slot * kAtoms + (ks >> 2)) * kAtomBytesStat + (ks & 3) * 32) >> 4);
+      };
+      auto strm_desc_k = [&](uint32_t stage, int slot, int ks) {   // K-major B
+        return smem_desc_sw128(stage, 16, 1024) + (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4);
+      };
+      auto strm_desc_mn = [&](uint32_t stage, int slot, int ks) {  // MN-major B, 16 rows per k-step
+        return smem_desc_sw128(stage, CF::stream_atom_stride(slot), 1024) +
+               (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4);
+      };
+      // operand written by the math warps over RB: the 16 elements of k-step ks sit in 8
+      // columns at col0 + 32*(ks/2) + 8*(ks%2) (owner half, then chunk)
+      auto op_tmem = [&](int col0, int ks) { return tmem_base + (uint32_t)(col0 + 32 * (ks >> 1) + 8 * (ks & 1)); };
+      auto ss = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ss(d, a, b, idesc, acc);
+      };
+      auto ts = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ts(d, a, b, idesc, acc);
+      };
+      auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
+      constexpr int KS = D / 16, KO = BN / 16;
+      const uint32_t ra = tmem_base + CF::kRA, rb = tmem_base + CF::kRB;
+      const uint32_t out0 = tmem_base + CF::kOut0, out1 = tmem_base + CF::kOut1;
+
+      auto issue_ra = [&](uint32_t stage) {
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S^T | K g_dQ^T] = K [Q; g_dQ]^T
+          ss(ra, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS^T += g_dK Q^T
+          ss(ra + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+      };
+      auto issue_rb = [&](uint32_t stage) {
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // dP^T = V dO^T
+          ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gPdV^T = g_dV dO^T
+          ss(rb + 64, stat_desc(3, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
+      };
+      auto issue_out = [&](uint32_t stage, bool first) {    // operands: dS^T at RB, g_dp^T at RB+16, g_S^T at RB+64
+        _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += dS^T g_dQ
+          ts(out0, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
+        _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += g_S^T Q
+          ts(out0, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
+        _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_V += g_dp^T dO
+          ts(out1, op_tmem(CF::kRB + 16, ks), strm_desc_mn(stage, 2, ks), kIdescOut, !(first && ks == 0));
+      };
+
+      ok = ok && mbar_wait(bar_stream_full(0), 0, abort_flag, t.status, wait_code(KIND, 3));
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_ra(strm_base); commit(bar_ra_full);
+        issue_rb(strm_base); commit(bar_rb_full);
+      }
+      for (int j = 0; j < n_iter && ok; ++j) {
+        const int st = j & 1, nst = st ^ 1;
+        const bool more = j + 1 < n_iter;
+        if (more) {
+          // RA of tile j has been read: the next tile's RA products go first
+          ok = mbar_wait(bar_stream_full(nst), ((j + 1) >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
+          if (ok) ok = mbar_wait(bar_ra_free, j & 1, abort_flag, t.status, wait_code(KIND, 4));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_ra(strm_base + nst * CF::kStageBytes);
+          commit(bar_ra_full);
+        }
+        ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_out(strm_base + st * CF::kStageBytes, j == 0);
+        commit(bar_stream_empty(st));
+        if (more) {
+          issue_rb(strm_base + nst * CF::kStageBytes);   // after the outputs that read RB (in order)
+          commit(bar_rb_full);
+        }
+      }
+      if (ok) commit(bar_acc_done);
+    }
+  }
+  // =========================================================================
+  // math warps
+  // =========================================================================
+  else {
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;       // key row within the tile == TMEM lane
+    const int gidx = r0 + row;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const size_t row_off = (size_t)bh * g.N_q;
+
+    int vlo, vhi;                              // query rows that see this thread's key row
+    query_range_for_keys(g, gidx, gidx + 1, vlo, vhi);
+    if (gidx >= g.N_kv) { vlo = 0; vhi = 0; }
+    const uint32_t vspan = (uint32_t)(vhi - vlo);
+    const float2 sl2 = make_float2(g.scale_log2e, g.scale_log2e);
+    const float2 sc2 = make_float2(g.scale, g.scale);
+    const uint32_t ra = lane_addr + CF::kRA, rb = lane_addr + CF::kRB;
+
+    float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int j0 = (t_begin + it) * BN;
+      // per-query scalars of the streamed tile, negated so that every use is a packed add / fma:
+      // [-L*log2(e) | -dot2 | -Dv | -(dot2*Dv + dot3)] x 64 queries; beyond N_q: -inf, 0, 0, 0 (p = 0)
+      const float* cs = col_stats + (it & 1) * 256;
+      {
+        const int which = threadIdx.x >> 6, c = threadIdx.x & 63;
+        const int qi = j0 + c;
+        float v = (which == 0) ? -INFINITY : 0.f;
+        if (qi < g.N_q) {
+          if (which == 0) v = -t.L[row_off + qi] * kLog2e;
+          else if (which == 1) v = -t.dot2[row_off + qi];
+          else if (which == 2) v = -t.Dv[row_off + qi];
+          else v = -fmaf(t.dot2[row_off + qi], t.Dv[row_off + qi], t.dot3[row_off + qi]);
+        }
+        col_stats[(it & 1) * 256 + which * 64 + c] = v;
+        __syncwarp();
+        const uint32_t bar = smem_u32(&ctl->stats_ready[it & 1]);
+        if (lane == 0) mbar_arrive(bar);
+        ok = mbar_wait(bar, (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 9));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      const int first = j0 + half * 32;
+      const bool masked = !(first >= vlo && first + 31 < vhi);
+
+      // ---------------- half-step 1: RA -> p, a ----------------------------------
+      ok = mbar_wait(bar_ra_full, it & 1, abort_flag, t.status, wait_code(KIND, 6));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      {
+        uint32_t s_[2][16], g_[2][16];
+        tmem_ld16(ra + half * 32, s_[0]);
+        tmem_ld16(ra + half * 32 + 16, s_[1]);
+        tmem_ld16(ra + 64 + half * 32, g_[0]);
+        tmem_ld16(ra + 64 + half * 32 + 16, g_[1]);
+        tmem_ld_wait(s_[0]);
+        tmem_ld_wait(s_[1]);
+        tmem_ld_wait(g_[0]);
+        tmem_ld_wait(g_[1]);
+        // the region may be overwritten by the next tile's products
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ra_free);
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const int cc = half * 32 + ch * 16 + e;
+            const float2 nL2 = *reinterpret_cast<const float2*>(cs + cc);
+            const float2 nD2 = *reinterpret_cast<const float2*>(cs + 64 + cc);
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(s_[ch][e]), __uint_as_float(s_[ch][e + 1])), sl2, nL2);
+            float2 pp = make_float2(ex2(x.x), ex2(x.y));
+            if (masked) {
+              pp.x = ((uint32_t)(j0 + cc - vlo) < vspan) ? pp.x : 0.f;
+              pp.y = ((uint32_t)(j0 + cc + 1 - vlo) < vspan) ? pp.y : 0.f;
+            }
+            p_[ch * 8 + (e >> 1)] = pp;
+            a_[ch * 8 + (e >> 1)] =
+                __ffma2_rn(make_float2(__uint_as_float(g_[ch][e]), __uint_as_float(g_[ch][e + 1])), sc2, nD2);
+          }
+      }
+
+      // ---------------- half-step 2: RB -> operands dS, g_dp, g_S ------------------
+      ok = mbar_wait(bar_rb_full, it & 1, abort_flag, t.status, wait_code(KIND, 7));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      {
+        uint32_t dp_[2][16], gp_[2][16];
+        tmem_ld16(rb + half * 32, dp_[0]);
+        tmem_ld16(rb + half * 32 + 16, dp_[1]);
+        tmem_ld16(rb + 64 + half * 32, gp_[0]);
+        tmem_ld16(rb + 64 + half * 32 + 16, gp_[1]);
+        tmem_ld_wait(dp_[0]);
+        tmem_ld_wait(dp_[1]);
+        tmem_ld_wait(gp_[0]);
+        tmem_ld_wait(gp_[1]);
+        // All of this thread's RB columns have been read; the operands go over them:
+        // dS at [32h, 32h+16), g_dp at [32h+16, 32h+32), g_S at [64+32h, 64+32h+16).
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t kds[8], kgdp[8], kgs[8];
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const int cc = half * 32 + ch * 16 + e;
+            const float2 nDv = *reinterpret_cast<const float2*>(cs + 128 + cc);
+            const float2 nC3 = *reinterpret_cast<const float2*>(cs + 192 + cc);
+            const float2 pp = p_[ch * 8 + (e >> 1)], aa = a_[ch * 8 + (e >> 1)];
+            const float2 dpd = __fadd2_rn(make_float2(__uint_as_float(dp_[ch][e]), __uint_as_float(dp_[ch][e + 1])), nDv);
+            const float2 ds = __fmul2_rn(pp, dpd);
+            const float2 gdp = __fmul2_rn(pp, aa);
+            const float2 tt = __fadd2_rn(make_float2(__uint_as_float(gp_[ch][e]), __uint_as_float(gp_[ch][e + 1])), nC3);
+            const float2 gs = __fmul2_rn(pp, __ffma2_rn(aa, dpd, tt));
+            kds[e >> 1] = Pack<T>::pack(ds.x, ds.y);
+            kgdp[e >> 1] = Pack<T>::pack(gdp.x, gdp.y);
+            kgs[e >> 1] = Pack<T>::pack(gs.x, gs.y);
+          }
+          tmem_st8(rb + half * 32 + ch * 8, kds);
+          tmem_st8(rb + half * 32 + 16 + ch * 8, kgdp);
+          tmem_st8(rb + 64 + half * 32 + ch * 8, kgs);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_op_full);
+    }
+
+    // ---------------- outputs --------------------------------------------------------
+    if (n_iter > 0 && ok) ok = mbar_wait(bar_acc_done, 0, abort_flag, t.status, wait_code(KIND, 8));
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after_sync();
+    constexpr int kColsPerHalf = D / 2;
+#pragma unroll
+    for (int o = 0; o < 2; ++o) {
+      T* dst = (T*)(o == 0 ? t.out_g_K : t.out_g_V);
+      const float mul = (o == 0) ? g.scale : 1.f;
+      T* prow = dst + ((size_t)bh * g.N_kv + gidx) * D + half * kColsPerHalf;
+#pragma unroll
+      for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
+        uint32_t v[16];
+        if (n_iter > 0 && ok) {
+          tmem_ld16(lane_addr + (o == 0 ? CF::kOut0 : CF::kOut1) + half * kColsPerHalf + ch * 16, v);
+          tmem_ld_wait(v);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = 0u;
+        }
+        if (gidx < g.N_kv) {
+          uint4 w0, w1;
+          w0.x = Pack<T>::pack(__uint_as_float(v[0]) * mul, __uint_as_float(v[1]) * mul);
+          w0.y = Pack<T>::pack(__uint_as_float(v[2]) * mul, __uint_as_float(v[3]) * mul);
+          w0.z = Pack<T>::pack(__uint_as_float(v[4]) * mul, __uint_as_float(v[5]) * mul);
+          w0.w = Pack<T>::pack(__uint_as_float(v[6]) * mul, __uint_as_float(v[7]) * mul);
+          w1.x = Pack<T>::pack(__uint_as_float(v[8]) * mul, __uint_as_float(v[9]) * mul);
+          w1.y = Pack<T>::pack(__uint_as_float(v[10]) * mul, __uint_as_float(v[11]) * mul);
+          w1.z = Pack<T>::pack(__uint_as_float(v[12]) * mul, __uint_as_float(v[13]) * mul);
+          w1.w = Pack<T>::pack(__uint_as_float(v[14]) * mul, __uint_as_float(v[15]) * mul);
+          reinterpret_cast<uint4*>(prow + ch * 16)[0] = w0;
+          reinterpret_cast<uint4*>(prow + ch * 16)[1] = w1;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kColMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int D, typename T>
+static cudaError_t launch_col(const TmaMaps& maps, const Geometry& g_in, const Tensors& t, cudaStream_t s) {
+  using CF = ColCfg<D>;
+  Geometry g = g_in;
+  const long long ctas = (long long)g.BH * ((g.N_kv + BM - 1) / BM);
+  if (ctas <= 0) return cudaSuccess;
+  if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  g.tile_major = ctas < 8 * 148 ? 1 : 0;
+  // more than half of an SM's shared memory: one CTA per SM, so the 512-column
+  // tensor-memory allocation never waits for a co-resident CTA
+  const size_t smem = CF::kSmemBytes < 122880u ? 122880u : CF::kSmemBytes;
+  auto kern = hvp_col_kernel<D, T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<(unsigned)ctas, kColThreads, smem, s>>>(maps, g, t);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_hvp_col(int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
+                           cudaStream_t s) {
+  if (D == 64) return is_bf16 ? launch_col<64, __nv_bfloat16>(maps, g, t, s) : launch_col<64, __half>(maps, g, t, s);
+  return is_bf16 ? launch_col<128, __nv_bfloat16>(maps, g, t, s) : launch_col<128, __half>(maps, g, t, s);
+}
+
+}  // namespace tc
+}  // namespace attn
