@@ -1,0 +1,577 @@
+// Forward and first-backward attention kernels on sm_100a (f16/bf16, D = 64 or 128).
+//
+// Four kinds of one kernel.  A CTA owns 128 STATIONARY rows of one (batch, head) and streams
+// 64-row tiles of the other axis through four TMA stages:
+//
+//   kind      stationary     streamed   tensor-memory score regions        produces
+//   FWD_LSE   Q              K          RA = S                 (x2)        L = log-sum-exp
+//   FWD_OUT   Q              K, V       RA = S                 (x2)        O = P V
+//   BWD_ROW   Q, dO          K, V       RA = S, RB = dP        (x2 each)   dQ = s dS K
+//   BWD_COL   K, V           Q, dO      RA = S^T, RB = dP^T    (x1 each)   dV = P^T dO, dK = s dS^T Q
+//
+// The stationary operands are copied once from shared memory into TENSOR MEMORY and serve from
+// there as the A operand of every score product (a stationary operand left in shared memory
+// would be re-read by each MMA instruction, and shared-memory operand bandwidth is the scarce
+// resource).  The math warps read a score region with tcgen05.ld, and write the half-precision
+// operands of the output products (P, dS) back over the score columns they have read; the output
+// products take them from there as their A operand.  The two-pass forward (L first, then
+// P = exp(S - L)) needs no running-maximum rescaling of O; every kind evaluates P the same way.
+// BWD_COL computes transposed scores (keys on the TMEM lanes) so that operand roles are the same
+// as in the row kinds; its per-query scalars (L, Dv) are staged in shared memory per tile.
+// One warp issues every MMA; with two buffers per region the score products run two tiles ahead.
+// Reference kernels: csrc/flash_double_backward_v7.cu:307-552 (forward), :649-1016 (backward).
+#include "attn_launch.h"
+#include "tc_common.cuh"
+
+namespace attn {
+namespace tc {
+
+enum FbKind { FB_FWD_LSE = 0, FB_FWD_OUT, FB_BWD_ROW, FB_BWD_COL };
+
+constexpr int kFbMmaWarp = 9;
+constexpr int kFbThreads = 320;
+constexpr int kFbStages = 4;
+
+struct FbControl {
+  uint64_t staging_full;
+  uint64_t stat_ready;
+  uint64_t stream_full[kFbStages];
+  uint64_t stream_empty[kFbStages];
+  uint64_t ra_full[2];
+  uint64_t rb_full[2];
+  uint64_t op_full[2];       // math warps are done with the regions of a tile (operands written)
+  uint64_t ra_free;          // BWD_COL only: RA has been read (before the tile is finished)
+  uint64_t acc_done;
+  uint64_t stats_ready[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+template <int KIND, int D>
+struct FbCfg {
+  static constexpr bool kCol = (KIND == FB_BWD_COL);
+  static constexpr bool kBwd = (KIND == FB_BWD_ROW || KIND == FB_BWD_COL);
+  static constexpr int kAtoms = D / 64;
+  static constexpr int kNStat = kBwd ? 2 : 1;
+  static constexpr int kNStream = (KIND == FB_FWD_LSE) ? 1 : 2;
+  static constexpr int kBufs = kCol ? 1 : 2;
+  static constexpr int kNOut = (KIND == FB_FWD_LSE) ? 0 : kCol ? 2 : 1;
+  static constexpr uint32_t kStagingBytes = kNStat * kAtoms * kAtomBytesStat;
+  static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
+  static constexpr uint32_t kAuxBytes = 512 + 2048;   // control; per-query scalars / L exchange
+  static constexpr uint32_t kContentBytes = kStagingBytes + kFbStages * kStageBytes + kAuxBytes;
+  static constexpr uint32_t kSmemBytes = kContentBytes + 1024;
+  // tensor-memory columns
+  static constexpr int kRA = 0;
+  static constexpr int kRB = kCol ? 64 : 128;
+  static constexpr int kStat = kCol ? 128 : 384;      // stationary operand x at kStat + 64 x
+  static constexpr int kOut = 256;
+  static_assert(kOut + kNOut * D <= (kCol ? 512 : 384), "tensor memory over-subscribed");
+  __host__ __device__ static constexpr uint32_t stream_off(int slot, int atom) {
+    return (uint32_t)(slot * kAtoms + atom) * kAtomBytesStrm;
+  }
+  __host__ __device__ static constexpr int stat_tensor(int x) { return kCol ? (x == 0 ? T_K : T_V) : (x == 0 ? T_Q : T_dO); }
+  __host__ __device__ static constexpr int stream_tensor(int s) { return kCol ? (s == 0 ? T_Q : T_dO) : (s == 0 ? T_K : T_V); }
+};
+
+template <int KIND, int D, typename T>
+__global__ void __launch_bounds__(kFbThreads, 1)
+fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors t) {
+  using CF = FbCfg<KIND, D>;
+  constexpr int kAtoms = CF::kAtoms;
+  constexpr int kBufs = CF::kBufs;
+  constexpr int KCODE = 16 + KIND;     // kernel id inside device status codes
+  constexpr uint32_t kIdesc64 = make_idesc(BM, 64, Pack<T>::kIsBf16, 0, 0);
+  constexpr uint32_t kIdescOut = make_idesc(BM, D, Pack<T>::kIsBf16, 0, 1);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  {
+    uint32_t dyn_size;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    if (smem_base - smem_u32(smem_raw) + CF::kContentBytes > dyn_size) {   // uniform over the CTA
+      if (threadIdx.x == 0 && t.status != nullptr) atomicCAS(t.status, 0u, wait_code(KCODE, 15));
+      return;
+    }
+  }
+  const uint32_t staging = smem_base;
+  const uint32_t strm_base = staging + CF::kStagingBytes;
+  const uint32_t aux_off = CF::kStagingBytes + kFbStages * CF::kStageBytes;
+  FbControl* ctl = reinterpret_cast<FbControl*>(smem_gen + aux_off);
+  float* aux_f = reinterpret_cast<float*>(smem_gen + aux_off + 512);   // 512 floats
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_stat = CF::kCol ? g.N_kv : g.N_q;
+  const int tiles = (n_stat + BM - 1) / BM;
+  const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
+  const int rank = g.tile_major ? (int)(blockIdx.x / g.BH) : (int)(blockIdx.x - bh * tiles);
+  const int tile = (CF::kCol || g.mask_mode != 0) ? rank : (tiles - 1 - rank);   // heavy tiles first
+  const int r0 = tile * BM;
+
+  int lo, hi;
+  if (CF::kCol) query_range_for_keys(g, r0, r0 + BM, lo, hi);
+  else key_range_for_queries(g, r0, r0 + BM, lo, hi);
+  const int t_begin = lo / BN;
+  const int n_iter = (hi > lo) ? ((hi + BN - 1) / BN - t_begin) : 0;
+
+  const uint32_t bar_staging_full = smem_u32(&ctl->staging_full), bar_stat_ready = smem_u32(&ctl->stat_ready);
+  const uint32_t bar_ra_free = smem_u32(&ctl->ra_free), bar_acc_done = smem_u32(&ctl->acc_done);
+  auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
+  auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
+  auto bar_ra_full = [&](int b) { return smem_u32(&ctl->ra_full[b]); };
+  auto bar_rb_full = [&](int b) { return smem_u32(&ctl->rb_full[b]); };
+  auto bar_op_full = [&](int b) { return smem_u32(&ctl->op_full[b]); };
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_staging_full, 1);
+    mbar_init(bar_stat_ready, kMathWarps);
+    for (int s = 0; s < kFbStages; ++s) {
+      mbar_init(bar_stream_full(s), 1);
+      mbar_init(bar_stream_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_ra_full(b), 1);
+      mbar_init(bar_rb_full(b), 1);
+      mbar_init(bar_op_full(b), kMathWarps);
+      mbar_init(smem_u32(&ctl->stats_ready[b]), kMathWarps);
+    }
+    mbar_init(bar_ra_free, kMathWarps);
+    mbar_init(bar_acc_done, 1);
+    ctl->abort_flag = 0u;
+    ctl->tmem_base = 0u;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (warp == kFbMmaWarp) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  // =========================================================================
+  // TMA producer
+  // =========================================================================
+  if (warp == kProducerWarp) {
+    if (lane == 0 && n_iter > 0) {
+      for (int i = 0; i < T_COUNT; ++i) tma_prefetch_desc(&maps.m[i]);
+      mbar_arrive_expect_tx(bar_staging_full, CF::kStagingBytes);
+#pragma unroll
+      for (int x = 0; x < CF::kNStat; ++x)
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            tma_load_3d(staging + (x * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm,
+                        &maps.m[CF::stat_tensor(x)], a * 64, r0 + h * 64, bh, bar_staging_full);
+      bool ok = true;
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it % kFbStages;
+        ok = mbar_wait(bar_stream_empty(st), ((it / kFbStages) & 1) ^ 1, abort_flag, t.status, wait_code(KCODE, 1));
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
+        const uint32_t stage = strm_base + st * CF::kStageBytes;
+#pragma unroll
+        for (int s = 0; s < CF::kNStream; ++s)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(stage + CF::stream_off(s, a), &maps.m[CF::stream_tensor(s)], a * 64,
+                        (t_begin + it) * BN, bh, bar_stream_full(st));
+      }
+      if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+      }
+    }
+  }
+  // =========================================================================
+  // MMA issuer (converged warp, one elected lane issues)
+  // =========================================================================
+  else if (warp == kFbMmaWarp) {
+    if (n_iter > 0) {
+      bool ok = mbar_wait(bar_stat_ready, 0, abort_flag, t.status, wait_code(KCODE, 2));
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after_sync();
+      auto strm_desc_k = [&](uint32_t stage, int slot, int ks) {   // K-major B
+        return smem_desc_sw128(stage, 16, 1024) + (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4);
+      };
+      auto strm_desc_mn = [&](uint32_t stage, int slot, int ks) {  // MN-major B, 16 rows per k-step
+        return smem_desc_sw128(stage, kAtomBytesStrm, 1024) + (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4);
+      };
+      // operand written by the math warps over a score region: the 16 elements of k-step ks sit in
+      // 8 columns at col0 + 32*(ks/2) + 8*(ks%2) (owner half, then chunk)
+      auto op_tmem = [&](int col0, int ks) { return tmem_base + (uint32_t)(col0 + 32 * (ks >> 1) + 8 * (ks & 1)); };
+      auto ts = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+        if (elect_one()) mma_ts(d, a, b, idesc, acc);
+      };
+      auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
+      constexpr int KS = D / 16, KO = BN / 16;
+      const uint32_t stat0 = tmem_base + CF::kStat, stat1 = stat0 + 64;
+      const uint32_t out0 = tmem_base + CF::kOut, out1 = out0 + D;
+      (void)stat1; (void)out1;
+
+      auto stage_of = [&](int j) { return strm_base + (uint32_t)(j % kFbStages) * CF::kStageBytes; };
+      auto wait_stream = [&](int j) {
+        bool w = mbar_wait(bar_stream_full(j % kFbStages), (j / kFbStages) & 1, abort_flag, t.status, wait_code(KCODE, 3));
+        return (bool)__all_sync(0xffffffffu, w);
+      };
+      auto issue_ra = [&](int j) {     // S = Q K^T   |   S^T = K Q^T
+        const int b = j % kBufs;
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          ts(tmem_base + CF::kRA + 64 * b, stat0 + 8 * ks, strm_desc_k(stage_of(j), 0, ks), kIdesc64, ks > 0);
+        commit(bar_ra_full(b));
+      };
+      auto issue_rb = [&](int j) {     // dP = dO V^T |   dP^T = V dO^T
+        const int b = j % kBufs;
+        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          ts(tmem_base + CF::kRB + 64 * b, stat1 + 8 * ks, strm_desc_k(stage_of(j), 1, ks), kIdesc64, ks > 0);
+        commit(bar_rb_full(b));
+      };
+      auto issue_out = [&](int j) {
+        const int b = j % kBufs;
+        const uint32_t stage = stage_of(j);
+        const bool first = (j == 0);
+        if constexpr (KIND == FB_FWD_OUT) {          // O += P V
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+            ts(out0, op_tmem(CF::kRA + 64 * b, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
+        } else if constexpr (KIND == FB_BWD_ROW) {   // dQ += dS K
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+            ts(out0, op_tmem(CF::kRB + 64 * b, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
+        } else if constexpr (KIND == FB_BWD_COL) {   // dV += P^T dO ; dK += dS^T Q
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+            ts(out0, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+            ts(out1, op_tmem(CF::kRB + 16, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
+        }
+      };
+
+      // score products run kBufs tiles ahead of the math warps
+      for (int i = 0; i < kBufs && i < n_iter && ok; ++i) {
+        ok = wait_stream(i);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_ra(i);
+        if constexpr (CF::kBwd) issue_rb(i);
+      }
+      for (int j = 0; j < n_iter && ok; ++j) {
+        const int b = j % kBufs;
+        if constexpr (CF::kCol) {
+          // single-buffered regions: S^T of the next tile as soon as this tile's has been read
+          if (j + 1 < n_iter) {
+            ok = wait_stream(j + 1);
+            if (ok) ok = mbar_wait(bar_ra_free, j & 1, abort_flag, t.status, wait_code(KCODE, 4));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_ra(j + 1);
+          }
+        }
+        ok = mbar_wait(bar_op_full(b), (j / kBufs) & 1, abort_flag, t.status, wait_code(KCODE, 5));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if constexpr (CF::kNOut > 0) issue_out(j);
+        commit(bar_stream_empty(j % kFbStages));    // every product reading this stage has been issued
+        const int nj = j + kBufs;
+        if (nj < n_iter) {
+          if constexpr (CF::kCol) {
+            issue_rb(nj);                           // after the outputs that read RB (in order)
+          } else {
+            ok = wait_stream(nj);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_ra(nj);                           // buffer b: read by tile j, its outputs issued above
+            if constexpr (CF::kBwd) issue_rb(nj);
+          }
+        }
+      }
+      if constexpr (CF::kNOut > 0) { if (ok) commit(bar_acc_done); }
+    }
+  }
+  // =========================================================================
+  // math warps
+  // =========================================================================
+  else {
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;         // stationary row within the tile == TMEM lane
+    const int gidx = r0 + row;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const size_t row_off = (size_t)bh * g.N_q;
+
+    int vlo, vhi;                                // streamed indices visible to this stationary row
+    if (CF::kCol) query_range_for_keys(g, gidx, gidx + 1, vlo, vhi);
+    else key_range_for_queries(g, gidx, gidx + 1, vlo, vhi);
+    if (gidx >= n_stat) { vlo = 0; vhi = 0; }
+    const uint32_t vspan = (uint32_t)(vhi - vlo);
+
+    // ---- one-time copy of the stationary rows from the staging buffer to tensor memory.
+    // Shared-memory tile: per 64-column atom, row r at r*128 bytes, 16-byte chunks XOR-swizzled
+    // by r % 8.  Tensor-memory A operand: lane = row, one 32-bit column per pair of K elements.
+    bool ok = true;
+    if (n_iter > 0) {
+      ok = mbar_wait(bar_staging_full, 0, abort_flag, t.status, wait_code(KCODE, 6));
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        constexpr int kChunksPerHalf = D / 16;
+#pragma unroll
+        for (int x = 0; x < CF::kNStat; ++x) {
+          const uint32_t src = staging + x * kAtoms * kAtomBytesStat;
+          const uint32_t dst = lane_addr + CF::kStat + 64 * x;
+#pragma unroll
+          for (int c = 0; c < kChunksPerHalf; c += 2) {
+            uint32_t w[8];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int gc = half * kChunksPerHalf + c + u;
+              const uint32_t addr = src + (gc >> 3) * kAtomBytesStat + row * 128 + ((((uint32_t)(gc & 7)) ^ (row & 7)) << 4);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(w[4 * u]), "=r"(w[4 * u + 1]), "=r"(w[4 * u + 2]), "=r"(w[4 * u + 3])
+                           : "r"(addr));
+            }
+            tmem_st8(dst + 4 * (half * kChunksPerHalf + c), w);
+          }
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_stat_ready);
+    }
+
+    // per-row scalars (row kinds), negated so that every use is a packed add / fma
+    float2 nL2 = make_float2(-INFINITY, -INFINITY), nDv = make_float2(0.f, 0.f);
+    if constexpr (KIND == FB_FWD_OUT || KIND == FB_BWD_ROW) {
+      if (gidx < g.N_q) {
+        const float L2 = t.L[row_off + gidx] * kLog2e;
+        nL2 = make_float2(-L2, -L2);
+        if constexpr (KIND == FB_BWD_ROW) { const float Dv = t.Dv[row_off + gidx]; nDv = make_float2(-Dv, -Dv); }
+      }
+    }
+    const float2 sl2 = make_float2(g.scale_log2e, g.scale_log2e);
+    float acc_m = -INFINITY, acc_l = 0.f;        // FWD_LSE: running maximum and sum (log2 domain)
+    float2 p_[16];                               // backward kinds: carried from S to dP
+
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int b = it % kBufs;
+      const int j0 = (t_begin + it) * BN;
+      const int first = j0 + half * 32;
+      const bool masked = !(first >= vlo && first + 31 < vhi);
+      const uint32_t ra = lane_addr + CF::kRA + 64 * b + half * 32;
+      const uint32_t rb = lane_addr + CF::kRB + 64 * b + half * 32;
+      const float* cs = aux_f + (it & 1) * 128;   // BWD_COL: [-L*log2(e) | -Dv] x 64 queries
+      if constexpr (CF::kCol) {
+        if (threadIdx.x < 128) {
+          const int which = threadIdx.x >> 6, c = threadIdx.x & 63;
+          const int qi = j0 + c;
+          float v = (which == 0) ? -INFINITY : 0.f;
+          if (qi < g.N_q) v = (which == 0) ? -t.L[row_off + qi] * kLog2e : -t.Dv[row_off + qi];
+          aux_f[(it & 1) * 128 + which * 64 + c] = v;
+        }
+        __syncwarp();
+        const uint32_t bar = smem_u32(&ctl->stats_ready[it & 1]);
+        if (lane == 0) mbar_arrive(bar);
+        ok = mbar_wait(bar, (it >> 1) & 1, abort_flag, t.status, wait_code(KCODE, 9));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+
+      // ---------------- scores: S -> p ------------------------------------------
+      ok = mbar_wait(bar_ra_full(b), (it / kBufs) & 1, abort_flag, t.status, wait_code(KCODE, 7));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t s_[2][16];
+      tmem_ld16(ra, s_[0]);
+      tmem_ld16(ra + 16, s_[1]);
+      tmem_ld_wait(s_[0]);
+      tmem_ld_wait(s_[1]);
+      if constexpr (CF::kCol) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ra_free);
+      }
+      if constexpr (KIND == FB_FWD_LSE) {
+        float x[32], mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const bool vis = !masked || ((uint32_t)(first + e - vlo) < vspan);
+          x[e] = vis ? __uint_as_float(s_[e >> 4][e & 15]) * g.scale_log2e : -INFINITY;
+          mx = fmaxf(mx, x[e]);
+        }
+        if (mx > -INFINITY) {
+          const float mn = fmaxf(acc_m, mx);
+          float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) { sum0 += ex2(x[e] - mn); sum1 += ex2(x[e + 1] - mn); }
+          acc_l = acc_l * ex2(acc_m - mn) + (sum0 + sum1);
+          acc_m = mn;
+        }
+      } else {
+        uint32_t kp[2][8];
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const int cc = half * 32 + ch * 16 + e;
+            float2 l2 = nL2;
+            if constexpr (CF::kCol) l2 = *reinterpret_cast<const float2*>(cs + cc);
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(s_[ch][e]), __uint_as_float(s_[ch][e + 1])), sl2, l2);
+            float2 pp = make_float2(ex2(x.x), ex2(x.y));
+            if (masked) {
+              pp.x = ((uint32_t)(j0 + cc - vlo) < vspan) ? pp.x : 0.f;
+              pp.y = ((uint32_t)(j0 + cc + 1 - vlo) < vspan) ? pp.y : 0.f;
+            }
+            p_[ch * 8 + (e >> 1)] = pp;
+            kp[ch][e >> 1] = Pack<T>::pack(pp.x, pp.y);
+          }
+        if constexpr (KIND == FB_FWD_OUT) {
+          // P over the S columns this thread has read
+          tmem_st8(ra, kp[0]);
+          tmem_st8(ra + 8, kp[1]);
+          tmem_st_wait();
+        } else {
+          // ---------------- dP -> dS (and P^T for the column kind) ------------------
+          ok = mbar_wait(bar_rb_full(b), (it / kBufs) & 1, abort_flag, t.status, wait_code(KCODE, 8));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          uint32_t d_[2][16];
+          tmem_ld16(rb, d_[0]);
+          tmem_ld16(rb + 16, d_[1]);
+          tmem_ld_wait(d_[0]);
+          tmem_ld_wait(d_[1]);
+          uint32_t kds[2][8];
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+            for (int e = 0; e < 16; e += 2) {
+              const int cc = half * 32 + ch * 16 + e;
+              float2 dv = nDv;
+              if constexpr (CF::kCol) dv = *reinterpret_cast<const float2*>(cs + 64 + cc);
+              const float2 dpd = __fadd2_rn(make_float2(__uint_as_float(d_[ch][e]), __uint_as_float(d_[ch][e + 1])), dv);
+              const float2 ds = __fmul2_rn(p_[ch * 8 + (e >> 1)], dpd);
+              kds[ch][e >> 1] = Pack<T>::pack(ds.x, ds.y);
+            }
+          // over the dP columns this thread has read: [P^T (column kind) | dS]
+          if constexpr (CF::kCol) {
+            tmem_st8(rb, kp[0]);
+            tmem_st8(rb + 8, kp[1]);
+            tmem_st8(rb + 16, kds[0]);
+            tmem_st8(rb + 24, kds[1]);
+          } else {
+            tmem_st8(rb, kds[0]);
+            tmem_st8(rb + 8, kds[1]);
+          }
+          tmem_st_wait();
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_op_full(b));
+    }
+
+    // ---------------- results ------------------------------------------------------
+    if constexpr (KIND == FB_FWD_LSE) {
+      float* xm = aux_f;            // [128]
+      float* xl = aux_f + 128;      // [128]
+      if (half == 1) { xm[row] = acc_m; xl[row] = acc_l; }
+      named_barrier_sync(1, kMathThreads);
+      if (half == 0 && gidx < g.N_q) {
+        const float m1 = xm[row], l1 = xl[row];
+        const float mt = fmaxf(acc_m, m1);
+        float L = -INFINITY;
+        if (mt > -INFINITY) {
+          const float lt = acc_l * ex2(acc_m - mt) + l1 * ex2(m1 - mt);
+          L = (mt + log2f(lt)) * kLn2;
+        }
+        t.out_L[row_off + gidx] = L;
+      }
+    } else {
+      if (n_iter > 0 && ok) ok = mbar_wait(bar_acc_done, 0, abort_flag, t.status, wait_code(KCODE, 10));
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after_sync();
+      constexpr int kColsPerHalf = D / 2;
+#pragma unroll
+      for (int o = 0; o < CF::kNOut; ++o) {
+        T* dst;
+        float mul = 1.f;
+        if constexpr (KIND == FB_FWD_OUT) dst = (T*)t.out_O;
+        else if constexpr (KIND == FB_BWD_ROW) { dst = (T*)t.out_dQ; mul = g.scale; }
+        else { dst = (T*)(o == 0 ? t.out_dV : t.out_dK); mul = (o == 0) ? 1.f : g.scale; }
+        T* prow = dst + ((size_t)bh * n_stat + gidx) * D + half * kColsPerHalf;
+#pragma unroll
+        for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
+          uint32_t v[16];
+          if (n_iter > 0 && ok) {
+            tmem_ld16(lane_addr + CF::kOut + o * D + half * kColsPerHalf + ch * 16, v);
+            tmem_ld_wait(v);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = 0u;
+          }
+          if (gidx < n_stat) {
+            uint4 w0, w1;
+            w0.x = Pack<T>::pack(__uint_as_float(v[0]) * mul, __uint_as_float(v[1]) * mul);
+            w0.y = Pack<T>::pack(__uint_as_float(v[2]) * mul, __uint_as_float(v[3]) * mul);
+            w0.z = Pack<T>::pack(__uint_as_float(v[4]) * mul, __uint_as_float(v[5]) * mul);
+            w0.w = Pack<T>::pack(__uint_as_float(v[6]) * mul, __uint_as_float(v[7]) * mul);
+            w1.x = Pack<T>::pack(__uint_as_float(v[8]) * mul, __uint_as_float(v[9]) * mul);
+            w1.y = Pack<T>::pack(__uint_as_float(v[10]) * mul, __uint_as_float(v[11]) * mul);
+            w1.z = Pack<T>::pack(__uint_as_float(v[12]) * mul, __uint_as_float(v[13]) * mul);
+            w1.w = Pack<T>::pack(__uint_as_float(v[14]) * mul, __uint_as_float(v[15]) * mul);
+            reinterpret_cast<uint4*>(prow + ch * 16)[0] = w0;
+            reinterpret_cast<uint4*>(prow + ch * 16)[1] = w1;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kFbMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int KIND, int D, typename T>
+static cudaError_t launch_fb(const TmaMaps& maps, const Geometry& g_in, const Tensors& t, cudaStream_t s) {
+  using CF = FbCfg<KIND, D>;
+  Geometry g = g_in;
+  const int n_stat = CF::kCol ? g.N_kv : g.N_q;
+  const long long ctas = (long long)g.BH * ((n_stat + BM - 1) / BM);
+  if (ctas <= 0) return cudaSuccess;
+  if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  g.tile_major = ctas < 8 * 148 ? 1 : 0;
+  // more than half of an SM's shared memory: one CTA per SM, so the 512-column
+  // tensor-memory allocation never waits for a co-resident CTA
+  const size_t smem = CF::kSmemBytes < 122880u ? 122880u : CF::kSmemBytes;
+  auto kern = fb_kernel<KIND, D, T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<(unsigned)ctas, kFbThreads, smem, s>>>(maps, g, t);
+  return cudaGetLastError();
+}
+
+template <int D, typename T>
+static cudaError_t launch_fb_kind(int kind, const TmaMaps& maps, const Geometry& g, const Tensors& t, cudaStream_t s) {
+  switch (kind) {
+    case FB_FWD_LSE: return launch_fb<FB_FWD_LSE, D, T>(maps, g, t, s);
+    case FB_FWD_OUT: return launch_fb<FB_FWD_OUT, D, T>(maps, g, t, s);
+    case FB_BWD_ROW: return launch_fb<FB_BWD_ROW, D, T>(maps, g, t, s);
+    default: return launch_fb<FB_BWD_COL, D, T>(maps, g, t, s);
+  }
+}
+
+// kind: 0 forward L, 1 forward O, 2 backward dQ, 3 backward dK and dV
+cudaError_t launch_fwd_bwd(int kind, int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
+                           cudaStream_t s) {
+  if (D == 64) return is_bf16 ? launch_fb_kind<64, __nv_bfloat16>(kind, maps, g, t, s) : launch_fb_kind<64, __half>(kind, maps, g, t, s);
+  return is_bf16 ? launch_fb_kind<128, __nv_bfloat16>(kind, maps, g, t, s) : launch_fb_kind<128, __half>(kind, maps, g, t, s);
+}
+
+}  // namespace tc
+}  // namespace attn
