@@ -61,7 +61,7 @@ int check_shape(const attn_shape_t* s) {
   if ((long long)s->B * s->H > (1LL << 24)) return fail(ATTN_EINVAL, "B * H too large");
   if (s->impl < ATTN_IMPL_AUTO || s->impl > ATTN_IMPL_TENSOR) return fail(ATTN_EINVAL, "impl %d unknown", s->impl);
   if (s->impl == ATTN_IMPL_TENSOR && !attn::tc_supported(s->dtype, s->D))
-    return fail(ATTN_EUNSUPPORTED, "tensor-core kernels need f16/bf16 and D in {64, 128}");
+    return fail(ATTN_EUNSUPPORTED, "tensor-core kernels need f16 or bf16 inputs");
   return ATTN_OK;
 }
 

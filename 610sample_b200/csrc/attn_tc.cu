@@ -245,7 +245,9 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
 
 }  // namespace tc
 
-bool tc_supported(int dtype, int D) { return (dtype == 0 || dtype == 1) && (D == 64 || D == 128); }
+// Head dimensions that are not 64 or 128 run in the next larger of the two tile widths: the TMA
+// loads fill the padding columns with zeros and the epilogues store g.D columns only.
+bool tc_supported(int dtype, int D) { return (dtype == 0 || dtype == 1) && D >= 16 && D <= 128 && D % 16 == 0; }
 
 cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s, int* launches,
                       const char** err, int phases) {

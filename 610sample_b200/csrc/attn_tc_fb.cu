@@ -500,9 +500,11 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         if constexpr (KIND == FB_FWD_OUT) dst = (T*)t.out_O;
         else if constexpr (KIND == FB_BWD_ROW) { dst = (T*)t.out_dQ; mul = g.scale; }
         else { dst = (T*)(o == 0 ? t.out_dV : t.out_dK); mul = (o == 0) ? 1.f : g.scale; }
-        T* prow = dst + ((size_t)bh * n_stat + gidx) * D + half * kColsPerHalf;
+        // D is the padded head dimension of the tiles; the tensors in global memory have g.D columns
+        T* prow = dst + ((size_t)bh * n_stat + gidx) * g.D + half * kColsPerHalf;
 #pragma unroll
         for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
+          if (half * kColsPerHalf + ch * 16 >= g.D) break;   // padding columns (uniform over the warp)
           uint32_t v[16];
           if (n_iter > 0 && ok) {
             tmem_ld16(lane_addr + CF::kOut + o * D + half * kColsPerHalf + ch * 16, v);
@@ -569,7 +571,7 @@ static cudaError_t launch_fb_kind(int kind, const TmaMaps& maps, const Geometry&
 // kind: 0 forward L, 1 forward O, 2 backward dQ, 3 backward dK and dV
 cudaError_t launch_fwd_bwd(int kind, int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
                            cudaStream_t s) {
-  if (D == 64) return is_bf16 ? launch_fb_kind<64, __nv_bfloat16>(kind, maps, g, t, s) : launch_fb_kind<64, __half>(kind, maps, g, t, s);
+  if (D <= 64) return is_bf16 ? launch_fb_kind<64, __nv_bfloat16>(kind, maps, g, t, s) : launch_fb_kind<64, __half>(kind, maps, g, t, s);
   return is_bf16 ? launch_fb_kind<128, __nv_bfloat16>(kind, maps, g, t, s) : launch_fb_kind<128, __half>(kind, maps, g, t, s);
 }
 

@@ -399,9 +399,11 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     for (int o = 0; o < 2; ++o) {
       T* dst = (T*)(o == 0 ? t.out_g_K : t.out_g_V);
       const float mul = (o == 0) ? g.scale : 1.f;
-      T* prow = dst + ((size_t)bh * g.N_kv + gidx) * D + half * kColsPerHalf;
+      // D is the padded head dimension of the tiles; the tensors in global memory have g.D columns
+      T* prow = dst + ((size_t)bh * g.N_kv + gidx) * g.D + half * kColsPerHalf;
 #pragma unroll
       for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
+        if (half * kColsPerHalf + ch * 16 >= g.D) break;   // padding columns (uniform over the warp)
         uint32_t v[16];
         if (n_iter > 0 && ok) {
           tmem_ld16(lane_addr + (o == 0 ? CF::kOut0 : CF::kOut1) + half * kColsPerHalf + ch * 16, v);
@@ -455,7 +457,7 @@ static cudaError_t launch_col(const TmaMaps& maps, const Geometry& g_in, const T
 
 cudaError_t launch_hvp_col(int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
                            cudaStream_t s) {
-  if (D == 64) return is_bf16 ? launch_col<64, __nv_bfloat16>(maps, g, t, s) : launch_col<64, __half>(maps, g, t, s);
+  if (D <= 64) return is_bf16 ? launch_col<64, __nv_bfloat16>(maps, g, t, s) : launch_col<64, __half>(maps, g, t, s);
   return is_bf16 ? launch_col<128, __nv_bfloat16>(maps, g, t, s) : launch_col<128, __half>(maps, g, t, s);
 }
 

@@ -498,9 +498,11 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     constexpr int kColsPerHalf = D / 2;
     T* dst = (T*)(MODE == ROW_PREDO ? t.out_g_dO : t.out_g_Q);
     const float mul = (MODE == ROW_PREDO) ? 1.f : g.scale;
-    const size_t elem0 = ((size_t)bh * g.N_q + gidx) * D + half * kColsPerHalf;
+    // D is the padded head dimension of the tiles; the tensors in global memory have g.D columns
+    const size_t elem0 = ((size_t)bh * g.N_q + gidx) * g.D + half * kColsPerHalf;
 #pragma unroll
     for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
+      if (half * kColsPerHalf + ch * 16 >= g.D) break;   // padding columns (uniform over the warp)
       uint32_t v[16];
       if (n_iter > 0 && ok) {
         tmem_ld16(lane_addr + CF::kOut + half * kColsPerHalf + ch * 16, v);
@@ -566,10 +568,10 @@ static cudaError_t launch_row(const TmaMaps& maps, const Geometry& g_in, const T
 cudaError_t launch_hvp_row(int mode, int D, int is_bf16, const TmaMaps& maps, const Geometry& g,
                            const Tensors& t, cudaStream_t s) {
   if (mode == 0) {
-    if (D == 64) return is_bf16 ? launch_row<ROW_PREDO, 64, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_PREDO, 64, __half>(maps, g, t, s);
+    if (D <= 64) return is_bf16 ? launch_row<ROW_PREDO, 64, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_PREDO, 64, __half>(maps, g, t, s);
     return is_bf16 ? launch_row<ROW_PREDO, 128, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_PREDO, 128, __half>(maps, g, t, s);
   }
-  if (D == 64) return is_bf16 ? launch_row<ROW_Q, 64, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_Q, 64, __half>(maps, g, t, s);
+  if (D <= 64) return is_bf16 ? launch_row<ROW_Q, 64, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_Q, 64, __half>(maps, g, t, s);
   return is_bf16 ? launch_row<ROW_Q, 128, __nv_bfloat16>(maps, g, t, s) : launch_row<ROW_Q, 128, __half>(maps, g, t, s);
 }
 

@@ -52,8 +52,8 @@ def test_pointer_validation_and_unsupported_tensor_impl():
     assert lib.attn_b200_forward(s, None, 16, 16, 16, 16, None) == -1        # null pointer
     assert lib.attn_b200_forward(s, 8, 16, 16, 16, 16, None) == -1           # misaligned pointer
     assert lib.attn_b200_forward(None, 16, 16, 16, 16, 16, None) == -1       # null shape
-    s = capi.make_shape(1, 1, 64, 64, 80, 64, 0, 0, capi.ATTN_BF16, capi.IMPL_TENSOR)
-    assert lib.attn_b200_forward(s, 16, 16, 16, 16, 16, None) == -2          # no tensor-core kernel for D=80
+    s = capi.make_shape(1, 1, 64, 64, 144, 64, 0, 0, capi.ATTN_BF16, capi.IMPL_TENSOR)
+    assert lib.attn_b200_forward(s, 16, 16, 16, 16, 16, None) == -2          # head dimension above 128
     s = capi.make_shape(1, 1, 64, 64, 64, 64, 0, 0, capi.ATTN_F32, capi.IMPL_TENSOR)
     assert lib.attn_b200_forward(s, 16, 16, 16, 16, 16, None) == -2
 

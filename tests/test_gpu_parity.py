@@ -116,12 +116,28 @@ def test_ragged_and_edge_shapes_tensor(shape, dtype):
     check_half(got, oracle, dtype, str(shape))
 
 
+@pytest.mark.parametrize("impl", [1, 2])
 @pytest.mark.parametrize("D", [16, 48, 80, 96, 112])
-def test_other_head_dims_simt(D):
+def test_other_head_dims(D, impl):
+    """Head dimensions between the two tile widths (the reference builds 64, 80 and 96): the
+    tensor-core kernels run them zero-padded to the next tile width."""
     inp = orc.make_inputs(1, 2, 70, 150, D, seed=3, dtype=torch.bfloat16)
     oracle = orc.closed_form_all(*(inp[n] for n in orc.INPUT_NAMES), window_size=100, chunk_id=1)
-    got = run_all(inp, 100, 1, 0, 0)       # AUTO must pick the SIMT kernels here
+    got = run_all(inp, 100, 1, 0, impl)
     check_half(got, oracle, torch.bfloat16, f"D={D}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,cid", [(64, 0), (64, 3), (64, 7), (96, 5), (80, 8)])
+def test_chunked_sliding_window_shapes(D, cid, dtype):
+    """The reference's own workload (tests/test_ttt_e2e_bench.py:156-161): 1024 queries of chunk
+    `cid` against 9216 keys (8192 of history, left-padded while the history is shorter) under a
+    sliding window of 8192.  Two heads against the fp64 oracle."""
+    Nq, Nkv, ws = 1024, 9216, 8192
+    inp = orc.make_inputs(1, 2, Nq, Nkv, D, seed=11 + cid, dtype=dtype)
+    oracle = orc.closed_form_all(*(inp[n] for n in orc.INPUT_NAMES), window_size=ws, chunk_id=cid)
+    got = run_all(inp, ws, cid, 0, 0)
+    check_half(got, oracle, dtype, f"chunk {cid} D={D}")
 
 
 def test_bitwise_reproducible():
