@@ -77,7 +77,7 @@ attn::Geometry make_geometry(const attn_shape_t* s) {
   g.ki_base = s->chunk_id * s->N_q + s->N_q - s->N_kv;
   g.window = s->window_size > (1 << 30) ? (1 << 30) : s->window_size;
   g.mask_mode = s->mask_mode;
-  g.tile_major = 0;
+  g.head_group = 1;
   g.debug = 0;
 #ifdef ATTN_EXPERIMENT
   if (const char* e = getenv("ATTN_B200_DEBUG")) g.debug = atoi(e);

@@ -31,7 +31,10 @@ struct Geometry {
   int window;    // clamped to 2^30 so qi < ki + window never overflows
   int mask_mode; // 0 reference mask, 1 none
   int debug;       // experiment switches; only read by builds with ATTN_EXPERIMENT defined
-  int tile_major;  // CTA order: 0 = head-major (L2 locality), 1 = tile-major (balance on small grids)
+  // CTA order: heads are taken in groups of `head_group`; within a group the CTAs go tile by
+  // tile, heavy tiles first, over all heads of the group.  Large groups balance the SMs (longest
+  // work first), small groups keep the streamed tensors of the heads in flight inside the L2.
+  int head_group;
   float scale;       // 1/sqrt(D)
   float scale_log2e; // scale * log2(e)
 };
@@ -128,6 +131,30 @@ template <> struct Elem<__nv_bfloat16> {
 };
 
 // Pointer bundle shared by every launcher.  Unused members stay null.
+// blockIdx -> (head, rank of the tile within the head) under the grouped order
+__device__ __forceinline__ void cta_to_head_and_rank(const Geometry& g, int tiles, int& bh, int& rank) {
+  const int per_group = g.head_group * tiles;
+  const int grp = (int)(blockIdx.x / (unsigned)per_group);
+  const int rem = (int)(blockIdx.x - (unsigned)(grp * per_group));
+  const int first = grp * g.head_group;
+  const int gsize = min(g.head_group, g.BH - first);
+  rank = rem / gsize;
+  bh = first + (rem - rank * gsize);
+}
+
+// heads per group: as many as keep `streamed_bytes_per_head` of every head of the group within
+// about 16 MB of L2, all heads when the grid is small anyway
+inline int pick_head_group(long long ctas, int BH, long long streamed_bytes_per_head) {
+#ifdef ATTN_EXPERIMENT
+  if (const char* e = getenv("ATTN_B200_GROUP")) { int n = atoi(e); if (n >= 1) return n > BH ? BH : n; }
+#endif
+  if (ctas < 8 * 148) return BH > 0 ? BH : 1;
+  long long n = (16ll << 20) / (streamed_bytes_per_head > 0 ? streamed_bytes_per_head : 1);
+  if (n < 1) n = 1;
+  if (n > BH) n = BH;
+  return (int)n;
+}
+
 struct Tensors {
   const void *Q, *K, *V, *dO, *O, *g_dQ, *g_dK, *g_dV;   // inputs
   const float* L;                                        // [BH, N_q]

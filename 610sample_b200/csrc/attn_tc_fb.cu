@@ -82,7 +82,6 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
   constexpr int kBufs = CF::kBufs;
   constexpr int KCODE = 16 + KIND;     // kernel id inside device status codes
   constexpr uint32_t kIdesc64 = make_idesc(BM, 64, Pack<T>::kIsBf16, 0, 0);
-  constexpr uint32_t kIdescOut = make_idesc(BM, D, Pack<T>::kIsBf16, 0, 1);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -104,8 +103,8 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_stat = CF::kCol ? g.N_kv : g.N_q;
   const int tiles = (n_stat + BM - 1) / BM;
-  const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
-  const int rank = g.tile_major ? (int)(blockIdx.x / g.BH) : (int)(blockIdx.x - bh * tiles);
+  int bh, rank;
+  cta_to_head_and_rank(g, tiles, bh, rank);
   const int tile = (CF::kCol || g.mask_mode != 0) ? rank : (tiles - 1 - rank);   // heavy tiles first
   const int r0 = tile * BM;
 
@@ -194,20 +193,18 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
       bool ok = mbar_wait(bar_stat_ready, 0, abort_flag, t.status, wait_code(KCODE, 2));
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
-      auto strm_desc_k = [&](uint32_t stage, int slot, int ks) {   // K-major B
-        return smem_desc_sw128(stage, 16, 1024) + (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4);
-      };
-      auto strm_desc_mn = [&](uint32_t stage, int slot, int ks) {  // MN-major B, 16 rows per k-step
-        return smem_desc_sw128(stage, kAtomBytesStrm, 1024) + (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4);
-      };
+      // descriptor offsets (16-byte units) within a stage: K-major B, k-step ks of slot; MN-major B,
+      // 16 rows per k-step
+      auto koff = [](int slot, int ks) { return (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4); };
+      auto moff = [](int slot, int ks) { return (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4); };
       // operand written by the math warps over a score region: the 16 elements of k-step ks sit in
       // 8 columns at col0 + 32*(ks/2) + 8*(ks%2) (owner half, then chunk)
       auto op_tmem = [&](int col0, int ks) { return tmem_base + (uint32_t)(col0 + 32 * (ks >> 1) + 8 * (ks & 1)); };
-      auto ts = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-        if (elect_one()) mma_ts(d, a, b, idesc, acc);
-      };
       auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
       constexpr int KS = D / 16, KO = BN / 16;
+      // a head dimension below the tile width: skip the k-steps and output columns that are padding
+      const int ks_n = g.D >> 4;
+      const uint32_t idesc_out = make_idesc(BM, g.D, Pack<T>::kIsBf16, 0, 1);
       const uint32_t stat0 = tmem_base + CF::kStat, stat1 = stat0 + 64;
       const uint32_t out0 = tmem_base + CF::kOut, out1 = out0 + D;
       (void)stat1; (void)out1;
@@ -217,34 +214,49 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         bool w = mbar_wait(bar_stream_full(j % kFbStages), (j / kFbStages) & 1, abort_flag, t.status, wait_code(KCODE, 3));
         return (bool)__all_sync(0xffffffffu, w);
       };
+      // Every batch of products is issued by the elected lane inside one branch, with the
+      // descriptor of the stage built once: the instruction stream between two MMAs is an add.
       auto issue_ra = [&](int j) {     // S = Q K^T   |   S^T = K Q^T
         const int b = j % kBufs;
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-          ts(tmem_base + CF::kRA + 64 * b, stat0 + 8 * ks, strm_desc_k(stage_of(j), 0, ks), kIdesc64, ks > 0);
-        commit(bar_ra_full(b));
+        const uint64_t dk = smem_desc_sw128(stage_of(j), 16, 1024);
+        const uint32_t acc = tmem_base + CF::kRA + 64 * b;
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            if (ks < ks_n) mma_ts(acc, stat0 + 8 * ks, dk + koff(0, ks), kIdesc64, ks > 0);
+          mma_commit(bar_ra_full(b));
+        }
+        __syncwarp();
       };
       auto issue_rb = [&](int j) {     // dP = dO V^T |   dP^T = V dO^T
         const int b = j % kBufs;
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-          ts(tmem_base + CF::kRB + 64 * b, stat1 + 8 * ks, strm_desc_k(stage_of(j), 1, ks), kIdesc64, ks > 0);
-        commit(bar_rb_full(b));
+        const uint64_t dk = smem_desc_sw128(stage_of(j), 16, 1024);
+        const uint32_t acc = tmem_base + CF::kRB + 64 * b;
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            if (ks < ks_n) mma_ts(acc, stat1 + 8 * ks, dk + koff(1, ks), kIdesc64, ks > 0);
+          mma_commit(bar_rb_full(b));
+        }
+        __syncwarp();
       };
       auto issue_out = [&](int j) {
         const int b = j % kBufs;
-        const uint32_t stage = stage_of(j);
+        const uint64_t dm = smem_desc_sw128(stage_of(j), kAtomBytesStrm, 1024);
         const bool first = (j == 0);
-        if constexpr (KIND == FB_FWD_OUT) {          // O += P V
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
-            ts(out0, op_tmem(CF::kRA + 64 * b, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
-        } else if constexpr (KIND == FB_BWD_ROW) {   // dQ += dS K
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
-            ts(out0, op_tmem(CF::kRB + 64 * b, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
-        } else if constexpr (KIND == FB_BWD_COL) {   // dV += P^T dO ; dK += dS^T Q
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
-            ts(out0, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
-            ts(out1, op_tmem(CF::kRB + 16, ks), strm_desc_mn(stage, 0, ks), kIdescOut, !(first && ks == 0));
+        if (elect_one()) {
+          if constexpr (KIND == FB_FWD_OUT) {          // O += P V
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+              mma_ts(out0, op_tmem(CF::kRA + 64 * b, ks), dm + moff(1, ks), idesc_out, !(first && ks == 0));
+          } else if constexpr (KIND == FB_BWD_ROW) {   // dQ += dS K
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+              mma_ts(out0, op_tmem(CF::kRB + 64 * b, ks), dm + moff(0, ks), idesc_out, !(first && ks == 0));
+          } else if constexpr (KIND == FB_BWD_COL) {   // dV += P^T dO ; dK += dS^T Q
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+              mma_ts(out0, op_tmem(CF::kRB, ks), dm + moff(1, ks), idesc_out, !(first && ks == 0));
+            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+              mma_ts(out1, op_tmem(CF::kRB + 16, ks), dm + moff(0, ks), idesc_out, !(first && ks == 0));
+          }
         }
+        __syncwarp();
       };
 
       // score products run kBufs tiles ahead of the math warps
@@ -547,7 +559,7 @@ static cudaError_t launch_fb(const TmaMaps& maps, const Geometry& g_in, const Te
   const long long ctas = (long long)g.BH * ((n_stat + BM - 1) / BM);
   if (ctas <= 0) return cudaSuccess;
   if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
-  g.tile_major = ctas < 8 * 148 ? 1 : 0;
+  g.head_group = pick_head_group(ctas, g.BH, 2ll * (KIND == FB_BWD_COL ? g.N_q : g.N_kv) * g.D * 2);
   // more than half of an SM's shared memory: one CTA per SM, so the 512-column
   // tensor-memory allocation never waits for a co-resident CTA
   const size_t smem = CF::kSmemBytes < 122880u ? 122880u : CF::kSmemBytes;

@@ -76,7 +76,6 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   constexpr int kAtoms = CF::kAtoms;
   constexpr uint32_t kIdesc64 = make_idesc(BM, 64, Pack<T>::kIsBf16, 0, 0);
   constexpr uint32_t kIdesc128 = make_idesc(BM, 128, Pack<T>::kIsBf16, 0, 0);
-  constexpr uint32_t kIdescOut = make_idesc(BM, D, Pack<T>::kIsBf16, 0, 1);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -97,8 +96,8 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles = (g.N_kv + BM - 1) / BM;
-  const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
-  const int tile = g.tile_major ? (int)(blockIdx.x / g.BH) : (int)(blockIdx.x - bh * tiles);   // early key tiles are the heavy ones
+  int bh, tile;   // early key tiles are the heavy ones
+  cta_to_head_and_rank(g, tiles, bh, tile);
   const int r0 = tile * BM;
 
   int lo, hi;
@@ -184,46 +183,57 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       auto stat_desc = [&](int slot, int ks) {   // K-major A from shared memory
         return d_stat + (uint64_t)(((slot * kAtoms + (ks >> 2)) * kAtomBytesStat + (ks & 3) * 32) >> 4);
       };
-      auto strm_desc_k = [&](uint32_t stage, int slot, int ks) {   // K-major B
-        return smem_desc_sw128(stage, 16, 1024) + (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4);
-      };
-      auto strm_desc_mn = [&](uint32_t stage, int slot, int ks) {  // MN-major B, 16 rows per k-step
-        return smem_desc_sw128(stage, CF::stream_atom_stride(slot), 1024) +
-               (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4);
-      };
+      // descriptor offsets (16-byte units) within a stage: K-major B, k-step ks of slot; MN-major B,
+      // 16 rows per k-step
+      auto koff = [](int slot, int ks) { return (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4); };
+      auto moff = [](int slot, int ks) { return (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4); };
       // operand written by the math warps over RB: the 16 elements of k-step ks sit in 8
       // columns at col0 + 32*(ks/2) + 8*(ks%2) (owner half, then chunk)
       auto op_tmem = [&](int col0, int ks) { return tmem_base + (uint32_t)(col0 + 32 * (ks >> 1) + 8 * (ks & 1)); };
-      auto ss = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-        if (elect_one()) mma_ss(d, a, b, idesc, acc);
-      };
-      auto ts = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-        if (elect_one()) mma_ts(d, a, b, idesc, acc);
-      };
       auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
       constexpr int KS = D / 16, KO = BN / 16;
+      // a head dimension below the tile width: skip the k-steps and output columns that are padding
+      const int ks_n = g.D >> 4;
+      const uint32_t idesc_out = make_idesc(BM, g.D, Pack<T>::kIsBf16, 0, 1);
       const uint32_t ra = tmem_base + CF::kRA, rb = tmem_base + CF::kRB;
       const uint32_t out0 = tmem_base + CF::kOut0, out1 = tmem_base + CF::kOut1;
 
+      // Every batch of products is issued by the elected lane inside one branch, with the
+      // descriptor of the stage built once: the instruction stream between two MMAs is an add.
       auto issue_ra = [&](uint32_t stage) {
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S^T | K g_dQ^T] = K [Q; g_dQ]^T
-          ss(ra, stat_desc(0, ks), strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS^T += g_dK Q^T
-          ss(ra + 64, stat_desc(2, ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S^T | K g_dQ^T] = K [Q; g_dQ]^T
+            if (ks < ks_n) mma_ss(ra, stat_desc(0, ks), dk + koff(0, ks), kIdesc128, ks > 0);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS^T += g_dK Q^T
+            if (ks < ks_n) mma_ss(ra + 64, stat_desc(2, ks), dk + koff(0, ks), kIdesc64, 1);
+        }
+        __syncwarp();
       };
       auto issue_rb = [&](uint32_t stage) {
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // dP^T = V dO^T
-          ss(rb, stat_desc(1, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gPdV^T = g_dV dO^T
-          ss(rb + 64, stat_desc(3, ks), strm_desc_k(stage, 2, ks), kIdesc64, ks > 0);
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // dP^T = V dO^T
+            if (ks < ks_n) mma_ss(rb, stat_desc(1, ks), dk + koff(2, ks), kIdesc64, ks > 0);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gPdV^T = g_dV dO^T
+            if (ks < ks_n) mma_ss(rb + 64, stat_desc(3, ks), dk + koff(2, ks), kIdesc64, ks > 0);
+        }
+        __syncwarp();
       };
       auto issue_out = [&](uint32_t stage, bool first) {    // operands: dS^T at RB, g_dp^T at RB+16, g_S^T at RB+64
-        _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += dS^T g_dQ
-          ts(out0, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
-        _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += g_S^T Q
-          ts(out0, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
-        _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_V += g_dp^T dO
-          ts(out1, op_tmem(CF::kRB + 16, ks), strm_desc_mn(stage, 2, ks), kIdescOut, !(first && ks == 0));
+        // the atoms of Q and g_dQ are interleaved, those of dO follow one another
+        const uint64_t dm01 = smem_desc_sw128(stage, CF::stream_atom_stride(0), 1024);
+        const uint64_t dm2 = smem_desc_sw128(stage, CF::stream_atom_stride(2), 1024);
+        static_assert(CF::stream_atom_stride(0) == CF::stream_atom_stride(1), "Q and g_dQ share a layout");
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += dS^T g_dQ
+            mma_ts(out0, op_tmem(CF::kRB, ks), dm01 + moff(1, ks), idesc_out, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += g_S^T Q
+            mma_ts(out0, op_tmem(CF::kRB + 64, ks), dm01 + moff(0, ks), idesc_out, 1);
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_V += g_dp^T dO
+            mma_ts(out1, op_tmem(CF::kRB + 16, ks), dm2 + moff(2, ks), idesc_out, !(first && ks == 0));
+        }
+        __syncwarp();
       };
 
       ok = ok && mbar_wait(bar_stream_full(0), 0, abort_flag, t.status, wait_code(KIND, 3));
@@ -444,7 +454,7 @@ static cudaError_t launch_col(const TmaMaps& maps, const Geometry& g_in, const T
   const long long ctas = (long long)g.BH * ((g.N_kv + BM - 1) / BM);
   if (ctas <= 0) return cudaSuccess;
   if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
-  g.tile_major = ctas < 8 * 148 ? 1 : 0;
+  g.head_group = pick_head_group(ctas, g.BH, 3ll * g.N_q * g.D * 2);   // Q, g_dQ, dO
   // more than half of an SM's shared memory: one CTA per SM, so the 512-column
   // tensor-memory allocation never waits for a co-resident CTA
   const size_t smem = CF::kSmemBytes < 122880u ? 122880u : CF::kSmemBytes;

@@ -98,7 +98,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   constexpr int kAtoms = CF::kAtoms;
   constexpr uint32_t kIdesc64 = make_idesc(BM, 64, Pack<T>::kIsBf16, 0, 0);
   constexpr uint32_t kIdesc128 = make_idesc(BM, 128, Pack<T>::kIsBf16, 0, 0);
-  constexpr uint32_t kIdescOut = make_idesc(BM, D, Pack<T>::kIsBf16, 0, 1);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -122,8 +121,8 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles = (g.N_q + BM - 1) / BM;
-  const int bh = g.tile_major ? (int)(blockIdx.x % g.BH) : (int)(blockIdx.x / tiles);
-  const int rank = g.tile_major ? (int)(blockIdx.x / g.BH) : (int)(blockIdx.x - bh * tiles);
+  int bh, rank;
+  cta_to_head_and_rank(g, tiles, bh, rank);
   const int tile = (g.mask_mode != 0) ? rank : (tiles - 1 - rank);   // heavy tiles first
   const int r0 = tile * BM;
 
@@ -221,49 +220,54 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       auto gq_desc = [&](int ks) {   // K-major A from shared memory: the g_dQ tile
         return d_stat + (uint64_t)(((ks >> 2) * kAtomBytesStat + (ks & 3) * 32) >> 4);
       };
-      auto strm_desc_k = [&](uint32_t stage, int slot, int ks) {   // K-major B
-        return smem_desc_sw128(stage, 16, 1024) + (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4);
-      };
-      auto strm_desc_mn = [&](uint32_t stage, int slot, int ks) {  // MN-major B, 16 rows per k-step
-        return smem_desc_sw128(stage, 2u * kAtomBytesStrm, 1024) + (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4);
-      };
+      // descriptor offsets (16-byte units) within a stage: K-major B, k-step ks of slot; MN-major B,
+      // 16 rows per k-step
+      auto koff = [](int slot, int ks) { return (uint64_t)((CF::stream_off(slot, ks >> 2) + (ks & 3) * 32) >> 4); };
+      auto moff = [](int slot, int ks) { return (uint64_t)((CF::stream_off(slot, 0) + ks * 2048) >> 4); };
       // operand written by the math warps over a 64-column score slot: the 16 elements of
       // k-step ks sit in 8 columns at 32*(ks/2) + 8*(ks%2) (owner half, then chunk)
       auto op_tmem = [&](int col0, int ks) { return tmem_base + (uint32_t)(col0 + 32 * (ks >> 1) + 8 * (ks & 1)); };
-      auto ss = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-        if (elect_one()) mma_ss(d, a, b, idesc, acc);
-      };
-      auto ts = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-        if (elect_one()) mma_ts(d, a, b, idesc, acc);
-      };
       auto commit = [&](uint32_t bar) { if (elect_one()) mma_commit(bar); };
       constexpr int KS = D / 16, KO = BN / 16;
+      // a head dimension below the tile width: skip the k-steps and output columns that are padding
+      const int ks_n = g.D >> 4;
+      const uint32_t idesc_out = make_idesc(BM, g.D, Pack<T>::kIsBf16, 0, 1);
       const uint32_t out = tmem_base + CF::kOut;
       const uint32_t ra = tmem_base + CF::kRA, rb = tmem_base + CF::kRB;
       const uint32_t qt = tmem_base + CF::kQT, dot = tmem_base + CF::kDOT;
 
-      auto issue_ra = [&](uint32_t stage) {
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-          ts(ra, qt + 8 * ks, strm_desc_k(stage, 0, ks), kIdesc128, ks > 0);
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-          ss(ra + 64, gq_desc(ks), strm_desc_k(stage, 0, ks), kIdesc64, 1);
+      // Every batch of products is issued by the elected lane inside one branch, with the
+      // descriptor of the stage built once: the instruction stream between two MMAs is an add.
+      auto issue_ra = [&](uint32_t stage, int tr_tile) {
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            if (ks < ks_n) mma_ts(ra, qt + 8 * ks, dk + koff(0, ks), kIdesc128, ks > 0);
+          ROW_TRACE(tr_tile, 2);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
+        }
+        __syncwarp();
       };
       auto issue_rb = [&](uint32_t stage) {
-        _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
-          ts(rb, dot + 8 * ks, strm_desc_k(stage, 2, ks), kIdesc128, ks > 0);
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            if (ks < ks_n) mma_ts(rb, dot + 8 * ks, dk + koff(2, ks), kIdesc128, ks > 0);
+        }
+        __syncwarp();
       };
       auto issue_out = [&](uint32_t stage, bool first) {
-        if constexpr (MODE == ROW_PREDO) {
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += P g_dV
-            ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 3, ks), kIdescOut, !(first && ks == 0));
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_dO' += (P o gdS) V
-            ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 2, ks), kIdescOut, 1);
-        } else {
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += dS g_dK
-            ts(out, op_tmem(CF::kRB, ks), strm_desc_mn(stage, 1, ks), kIdescOut, !(first && ks == 0));
-          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)     // g_Q += g_S K
-            ts(out, op_tmem(CF::kRB + 64, ks), strm_desc_mn(stage, 0, ks), kIdescOut, 1);
+        const uint64_t dm = smem_desc_sw128(stage, 2u * kAtomBytesStrm, 1024);
+        constexpr int s0 = (MODE == ROW_PREDO) ? 3 : 1;     // g_dO' += P g_dV      | g_Q += dS g_dK
+        constexpr int s1 = (MODE == ROW_PREDO) ? 2 : 0;     // g_dO' += (P o gdS) V | g_Q += g_S K
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+            mma_ts(out, op_tmem(CF::kRB, ks), dm + moff(s0, ks), idesc_out, !(first && ks == 0));
+          _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
+            mma_ts(out, op_tmem(CF::kRB + 64, ks), dm + moff(s1, ks), idesc_out, 1);
         }
+        __syncwarp();
       };
 
       {
@@ -273,7 +277,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           ok = __all_sync(0xffffffffu, ok);
           if (ok) {
             tc_fence_after_sync();
-            issue_ra(strm_base); commit(bar_ra_full);
+            issue_ra(strm_base, 0); commit(bar_ra_full);
             issue_rb(strm_base); commit(bar_rb_full);
           }
           for (int j = 0; j < n_iter && ok; ++j) {
@@ -287,7 +291,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
               if (!ok) break;
               tc_fence_after_sync();
               if (lane == 0) ROW_TRACE(j + 1, 0);
-              issue_ra(strm_base + nst * CF::kStageBytes);
+              issue_ra(strm_base + nst * CF::kStageBytes, j + 1);
               commit(bar_ra_full);
               if (lane == 0) ROW_TRACE(j + 1, 1);
             }
@@ -553,7 +557,7 @@ static cudaError_t launch_row(const TmaMaps& maps, const Geometry& g_in, const T
   const long long ctas = (long long)g.BH * ((g.N_q + BM - 1) / BM);
   if (ctas <= 0) return cudaSuccess;
   if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
-  g.tile_major = ctas < 8 * 148 ? 1 : 0;
+  g.head_group = pick_head_group(ctas, g.BH, 4ll * g.N_kv * g.D * 2);   // K, g_dK, V, g_dV
   // more than half of an SM's shared memory: one CTA per SM, so the 512-column
   // tensor-memory allocation never waits for a co-resident CTA
   const size_t smem = CF::kSmemBytes < 122880u ? 122880u : CF::kSmemBytes;
