@@ -130,6 +130,29 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     fence_proxy_async_smem();
   }
   __syncthreads();
+  // the stationary tiles and the first streamed tile are requested before the tensor-memory
+  // allocation and the second barrier: their latency is the longest item of the prologue
+  if (warp == kProducerWarp && lane == 0 && n_iter > 0) {
+    mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
+    mbar_arrive_expect_tx(bar_stream_full(0), CF::kStageBytes);
+#pragma unroll
+    for (int s = 0; s < CF::kNStat; ++s) {
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(stat_base + (s * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm,
+                      &maps.m[CF::stat_tensor(s)], a * 64, r0 + h * 64, bh, bar_stat_full);
+      if (s == 0) {     // the first product needs K and the streamed tile
+#pragma unroll
+        for (int sl = 0; sl < CF::kNStream; ++sl)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(strm_base + CF::stream_off(sl, a), &maps.m[CF::stream_tensor(sl)], a * 64, t_begin * BN, bh,
+                        bar_stream_full(0));
+      }
+    }
+  }
   if (warp == kColMmaWarp) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
@@ -142,18 +165,8 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   // =========================================================================
   if (warp == kProducerWarp) {
     if (lane == 0 && n_iter > 0) {
-      for (int i = 0; i < T_COUNT; ++i) tma_prefetch_desc(&maps.m[i]);
-      mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
-#pragma unroll
-      for (int s = 0; s < CF::kNStat; ++s)
-#pragma unroll
-        for (int a = 0; a < kAtoms; ++a)
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-            tma_load_3d(stat_base + (s * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm,
-                        &maps.m[CF::stat_tensor(s)], a * 64, r0 + h * 64, bh, bar_stat_full);
       bool ok = true;
-      for (int it = 0; it < n_iter; ++it) {
+      for (int it = 1; it < n_iter; ++it) {     // tile 0 was requested above
         const int st = it & 1;
         ok = mbar_wait(bar_stream_empty(st), ((it >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
         if (!ok) break;
@@ -200,23 +213,44 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
       // Every batch of products is issued by the elected lane inside one branch, with the
       // descriptor of the stage built once: the instruction stream between two MMAs is an add.
-      auto issue_ra = [&](uint32_t stage) {
+      // The last kTail k-steps of a score batch are issued after the wait that follows the batch
+      // in program order: the wait's latency then falls while the tensor pipe still has work queued.
+      constexpr int kTail = (D == 128) ? 2 : 0;
+      auto issue_ra_head = [&](uint32_t stage) {
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S^T | K g_dQ^T] = K [Q; g_dQ]^T
             if (ks < ks_n) mma_ss(ra, stat_desc(0, ks), dk + koff(0, ks), kIdesc128, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS^T += g_dK Q^T
+          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)   // gdS^T += g_dK Q^T
             if (ks < ks_n) mma_ss(ra + 64, stat_desc(2, ks), dk + koff(0, ks), kIdesc64, 1);
         }
         __syncwarp();
       };
-      auto issue_rb = [&](uint32_t stage) {
+      auto issue_ra_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
+            if (ks < ks_n) mma_ss(ra + 64, stat_desc(2, ks), dk + koff(0, ks), kIdesc64, 1);
+          mma_commit(bar_ra_full);
+        }
+        __syncwarp();
+      };
+      auto issue_rb_head = [&](uint32_t stage) {
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // dP^T = V dO^T
             if (ks < ks_n) mma_ss(rb, stat_desc(1, ks), dk + koff(2, ks), kIdesc64, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gPdV^T = g_dV dO^T
+          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)   // gPdV^T = g_dV dO^T
             if (ks < ks_n) mma_ss(rb + 64, stat_desc(3, ks), dk + koff(2, ks), kIdesc64, ks > 0);
+        }
+        __syncwarp();
+      };
+      auto issue_rb_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
+            if (ks < ks_n) mma_ss(rb + 64, stat_desc(3, ks), dk + koff(2, ks), kIdesc64, ks > 0);
+          mma_commit(bar_rb_full);
         }
         __syncwarp();
       };
@@ -236,35 +270,51 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         __syncwarp();
       };
 
-      ok = ok && mbar_wait(bar_stream_full(0), 0, abort_flag, t.status, wait_code(KIND, 3));
-      ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
+      auto wait_stream = [&](int tile) {
+        bool w = mbar_wait(bar_stream_full(tile & 1), (tile >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
+        w = __all_sync(0xffffffffu, w);
         tc_fence_after_sync();
-        issue_ra(strm_base); commit(bar_ra_full);
-        issue_rb(strm_base); commit(bar_rb_full);
+        return w;
+      };
+      auto wait_ra_free = [&](int tile) {    // the math warps have read RA of `tile`
+        bool w = mbar_wait(bar_ra_free, tile & 1, abort_flag, t.status, wait_code(KIND, 4));
+        w = __all_sync(0xffffffffu, w);
+        tc_fence_after_sync();
+        return w;
+      };
+      // Order per tile j: wait stream(j+1) [RA(j+1) head] wait op_full(j) [RA(j+1) tail] [OUT(j)]
+      // [RB(j+1) head] wait ra_free(j+1) [RB(j+1) tail].  RB(j+1) follows OUT(j), which reads RB,
+      // in the pipe's order.  With two stream stages tile j+2 is only requested once OUT(j) has
+      // completed, so the wait for it stays at the top of the next iteration.
+      ok = ok && wait_stream(0);
+      if (ok) {
+        issue_ra_head(strm_base); issue_ra_tail(strm_base);
+        issue_rb_head(strm_base); issue_rb_tail(strm_base);
+        if (n_iter > 1) ok = wait_ra_free(0);
       }
       for (int j = 0; j < n_iter && ok; ++j) {
         const int st = j & 1, nst = st ^ 1;
         const bool more = j + 1 < n_iter;
+        const uint32_t nstage = strm_base + nst * CF::kStageBytes;
         if (more) {
-          // RA of tile j has been read: the next tile's RA products go first
-          ok = mbar_wait(bar_stream_full(nst), ((j + 1) >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
-          if (ok) ok = mbar_wait(bar_ra_free, j & 1, abort_flag, t.status, wait_code(KIND, 4));
-          ok = __all_sync(0xffffffffu, ok);
+          ok = wait_stream(j + 1);
           if (!ok) break;
-          tc_fence_after_sync();
-          issue_ra(strm_base + nst * CF::kStageBytes);
-          commit(bar_ra_full);
+          issue_ra_head(nstage);
         }
         ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
+        if (more) issue_ra_tail(nstage);
         issue_out(strm_base + st * CF::kStageBytes, j == 0);
         commit(bar_stream_empty(st));
         if (more) {
-          issue_rb(strm_base + nst * CF::kStageBytes);   // after the outputs that read RB (in order)
-          commit(bar_rb_full);
+          issue_rb_head(nstage);
+          if (j + 2 < n_iter) {
+            ok = wait_ra_free(j + 1);
+            if (!ok) break;
+          }
+          issue_rb_tail(nstage);
         }
       }
       if (ok) commit(bar_acc_done);

@@ -42,7 +42,7 @@ enum RowMode { ROW_PREDO = 0, ROW_Q = 1 };
 
 // Experiment builds record clock stamps of CTA 0: slot = tile * 16 + event.
 #ifdef ATTN_EXPERIMENT
-#define ROW_TRACE(tile_, ev_) do { if (t.trace != nullptr && blockIdx.x == 0 && (tile_) < 64) t.trace[(tile_) * 16 + (ev_)] = clock64(); } while (0)
+#define ROW_TRACE(tile_, ev_) do { if (t.trace != nullptr && blockIdx.x == (unsigned)g.debug && (tile_) < 64) t.trace[(tile_) * 16 + (ev_)] = clock64(); } while (0)
 #else
 #define ROW_TRACE(tile_, ev_) do { } while (0)
 #endif
@@ -120,6 +120,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   float* row_sums = reinterpret_cast<float*>(smem_gen);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) ROW_TRACE(0, 10);
   const int tiles = (g.N_q + BM - 1) / BM;
   int bh, rank;
   cta_to_head_and_rank(g, tiles, bh, rank);
@@ -159,6 +160,33 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     fence_proxy_async_smem();
   }
   __syncthreads();
+  // the stationary tiles and the first streamed tile are requested before the tensor-memory
+  // allocation and the second barrier: their latency is the longest item of the prologue
+  if (warp == kProducerWarp && lane == 0 && n_iter > 0) {
+    mbar_arrive_expect_tx(bar_staging_full, CF::kStageBytes);
+#pragma unroll
+    for (int x = 0; x < 2; ++x)       // Q then dO: they are copied to tensor memory first
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(staging + (x * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[x == 0 ? T_Q : T_dO],
+                      a * 64, r0 + h * 64, bh, bar_staging_full);
+    mbar_arrive_expect_tx(bar_stream_full(0), CF::kStageBytes);
+#pragma unroll
+    for (int sl = 0; sl < CF::kNStream; ++sl)
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a)
+        tma_load_3d(strm_base + CF::stream_off(sl, a), &maps.m[CF::stream_tensor(sl)], a * 64, t_begin * BN, bh,
+                    bar_stream_full(0));
+    mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
+#pragma unroll
+    for (int a = 0; a < kAtoms; ++a)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        tma_load_3d(stat_base + a * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[T_gQ], a * 64, r0 + h * 64, bh,
+                    bar_stat_full);
+  }
   if (warp == kRowMmaWarp) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
@@ -171,22 +199,8 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   // =========================================================================
   if (warp == kProducerWarp) {
     if (lane == 0 && n_iter > 0) {
-      for (int i = 0; i < T_COUNT; ++i) tma_prefetch_desc(&maps.m[i]);
-      mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
-      mbar_arrive_expect_tx(bar_staging_full, CF::kStageBytes);
-#pragma unroll
-      for (int a = 0; a < kAtoms; ++a)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          tma_load_3d(stat_base + a * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[T_gQ], a * 64, r0 + h * 64, bh,
-                      bar_stat_full);
-          tma_load_3d(staging + a * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[T_Q], a * 64, r0 + h * 64, bh,
-                      bar_staging_full);
-          tma_load_3d(staging + (kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[T_dO], a * 64,
-                      r0 + h * 64, bh, bar_staging_full);
-        }
       bool ok = true;
-      for (int it = 0; it < n_iter; ++it) {
+      for (int it = 1; it < n_iter; ++it) {     // tile 0 was requested above
         const int st = it % kRowStages;
         ok = mbar_wait(bar_stream_empty(st), ((it / kRowStages) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
         // the third stage doubles as the staging buffer of Q and dO until they are in tensor memory
@@ -238,22 +252,43 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
       // Every batch of products is issued by the elected lane inside one branch, with the
       // descriptor of the stage built once: the instruction stream between two MMAs is an add.
-      auto issue_ra = [&](uint32_t stage, int tr_tile) {
+      // The last kTail k-steps of a score batch are issued after the wait that follows the batch
+      // in program order: the wait's latency then falls while the tensor pipe still has work queued.
+      constexpr int kTail = (D == 128) ? 2 : 0;
+      auto issue_ra_head = [&](uint32_t stage, int tr_tile) {
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
             if (ks < ks_n) mma_ts(ra, qt + 8 * ks, dk + koff(0, ks), kIdesc128, ks > 0);
           ROW_TRACE(tr_tile, 2);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)
             if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
         }
         __syncwarp();
       };
-      auto issue_rb = [&](uint32_t stage) {
+      auto issue_ra_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
+            if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
+          mma_commit(bar_ra_full);
+        }
+        __syncwarp();
+      };
+      auto issue_rb_head = [&](uint32_t stage) {
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)
             if (ks < ks_n) mma_ts(rb, dot + 8 * ks, dk + koff(2, ks), kIdesc128, ks > 0);
+        }
+        __syncwarp();
+      };
+      auto issue_rb_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
+            if (ks < ks_n) mma_ts(rb, dot + 8 * ks, dk + koff(2, ks), kIdesc128, ks > 0);
+          mma_commit(bar_rb_full);
         }
         __syncwarp();
       };
@@ -270,48 +305,54 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         __syncwarp();
       };
 
-      {
-        {
-          // tile 0: both regions
-          ok = ok && mbar_wait(bar_stream_full(0), 0, abort_flag, t.status, wait_code(KIND, 3));
-          ok = __all_sync(0xffffffffu, ok);
-          if (ok) {
-            tc_fence_after_sync();
-            issue_ra(strm_base, 0); commit(bar_ra_full);
-            issue_rb(strm_base); commit(bar_rb_full);
-          }
-          for (int j = 0; j < n_iter && ok; ++j) {
-            const int st = j % kRowStages, nst = (j + 1) % kRowStages;
-            const bool more = j + 1 < n_iter;
-            if (more) {
-              // RA of tile j has been read: next tile's RA products first, the math warps wait for them
-              ok = mbar_wait(bar_stream_full(nst), ((j + 1) / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
-              if (ok) ok = mbar_wait(bar_ra_free, j & 1, abort_flag, t.status, wait_code(KIND, 4));
-              ok = __all_sync(0xffffffffu, ok);
-              if (!ok) break;
-              tc_fence_after_sync();
-              if (lane == 0) ROW_TRACE(j + 1, 0);
-              issue_ra(strm_base + nst * CF::kStageBytes, j + 1);
-              commit(bar_ra_full);
-              if (lane == 0) ROW_TRACE(j + 1, 1);
-            }
-            ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
-            ok = __all_sync(0xffffffffu, ok);
+      // wait for the streamed tile `tile` and for the math warps to have read RA of tile - 1
+      auto wait_for_ra = [&](int tile) {
+        bool w = mbar_wait(bar_stream_full(tile % kRowStages), (tile / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
+        if (w && tile > 0) w = mbar_wait(bar_ra_free, (tile - 1) & 1, abort_flag, t.status, wait_code(KIND, 4));
+        w = __all_sync(0xffffffffu, w);
+        tc_fence_after_sync();
+        return w;
+      };
+      // Order per tile j: [RA(j+1) head] wait op_full(j) [RA(j+1) tail] [OUT(j)] [RB(j+1) head]
+      // wait stream(j+2), ra_free(j+1) [RB(j+1) tail].  RB(j+1) follows OUT(j), which reads RB, in
+      // the pipe's order.
+      ok = ok && wait_for_ra(0);
+      if (ok) {
+        issue_ra_head(strm_base, 0); issue_ra_tail(strm_base);
+        issue_rb_head(strm_base); issue_rb_tail(strm_base);
+        if (n_iter > 1) ok = wait_for_ra(1);
+      }
+      for (int j = 0; j < n_iter && ok; ++j) {
+        const int st = j % kRowStages, nst = (j + 1) % kRowStages;
+        const bool more = j + 1 < n_iter;
+        const uint32_t nstage = strm_base + nst * CF::kStageBytes;
+        if (more) {
+          if (lane == 0) ROW_TRACE(j + 1, 0);
+          issue_ra_head(nstage, j + 1);
+        }
+        ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (more) {
+          issue_ra_tail(nstage);
+          if (lane == 0) ROW_TRACE(j + 1, 1);
+        }
+        if (lane == 0) ROW_TRACE(j, 4);
+        issue_out(strm_base + st * CF::kStageBytes, j == 0);
+        commit(bar_stream_empty(st));
+        if (lane == 0) ROW_TRACE(j, 5);
+        if (more) {
+          issue_rb_head(nstage);
+          if (j + 2 < n_iter) {
+            ok = wait_for_ra(j + 2);
             if (!ok) break;
-            tc_fence_after_sync();
-            if (lane == 0) ROW_TRACE(j, 4);
-            issue_out(strm_base + st * CF::kStageBytes, j == 0);
-            commit(bar_stream_empty(st));
-            if (lane == 0) ROW_TRACE(j, 5);
-            if (more) {
-              issue_rb(strm_base + nst * CF::kStageBytes);   // after the outputs that read RB (in order)
-              commit(bar_rb_full);
-              if (lane == 0) ROW_TRACE(j + 1, 3);
-            }
           }
-          if (ok) commit(bar_acc_done);
+          issue_rb_tail(nstage);
+          if (lane == 0) ROW_TRACE(j + 1, 3);
         }
       }
+      if (ok) commit(bar_acc_done);
     }
   }
   // =========================================================================
@@ -378,6 +419,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_stat_tmem_ready);
+      if (threadIdx.x == 0) ROW_TRACE(0, 11);
     }
 
     float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2 (ROW_PREDO: a_ = p * gdS)
@@ -496,33 +538,52 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         t.dot3[row_off + gidx] = A - 2.f * Dv * d2 + E;
       }
     }
-    if (n_iter > 0 && ok) ok = mbar_wait(bar_acc_done, 0, abort_flag, t.status, wait_code(KIND, 9));
-    ok = __all_sync(0xffffffffu, ok);
-    tc_fence_after_sync();
     constexpr int kColsPerHalf = D / 2;
+    constexpr int kChunks = kColsPerHalf / 16;
     T* dst = (T*)(MODE == ROW_PREDO ? t.out_g_dO : t.out_g_Q);
     const float mul = (MODE == ROW_PREDO) ? 1.f : g.scale;
     // D is the padded head dimension of the tiles; the tensors in global memory have g.D columns
     const size_t elem0 = ((size_t)bh * g.N_q + gidx) * g.D + half * kColsPerHalf;
+    // g_dO = g_dO' - dot2 * O: this thread's part of the O row is fetched while the last
+    // products are still running
+    uint4 o_[MODE == ROW_PREDO ? 2 * kChunks : 1];
+    if constexpr (MODE == ROW_PREDO) {
 #pragma unroll
-    for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
-      if (half * kColsPerHalf + ch * 16 >= g.D) break;   // padding columns (uniform over the warp)
-      uint32_t v[16];
+      for (int ch = 0; ch < kChunks; ++ch) {
+        const bool in = gidx < g.N_q && half * kColsPerHalf + ch * 16 < g.D;
+        const uint4* orow = reinterpret_cast<const uint4*>((const T*)t.O + elem0 + ch * 16);
+        o_[2 * ch] = in ? __ldg(orow) : make_uint4(0u, 0u, 0u, 0u);
+        o_[2 * ch + 1] = in ? __ldg(orow + 1) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    if (n_iter > 0 && ok) ok = mbar_wait(bar_acc_done, 0, abort_flag, t.status, wait_code(KIND, 9));
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after_sync();
+    if (threadIdx.x == 0) ROW_TRACE(0, 12);
+    // all accumulator columns of this thread first, then the arithmetic and the stores
+    uint32_t v[kChunks][16];
+#pragma unroll
+    for (int ch = 0; ch < kChunks; ++ch) {
       if (n_iter > 0 && ok) {
-        tmem_ld16(lane_addr + CF::kOut + half * kColsPerHalf + ch * 16, v);
-        tmem_ld_wait(v);
+        tmem_ld16(lane_addr + CF::kOut + half * kColsPerHalf + ch * 16, v[ch]);
       } else {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] = 0u;
+        for (int e = 0; e < 16; ++e) v[ch][e] = 0u;
       }
+    }
+    if (n_iter > 0 && ok) {
+#pragma unroll
+      for (int ch = 0; ch < kChunks; ++ch) tmem_ld_wait(v[ch]);
+    }
+#pragma unroll
+    for (int ch = 0; ch < kChunks; ++ch) {
+      if (half * kColsPerHalf + ch * 16 >= g.D) break;   // padding columns (uniform over the warp)
       if (gidx < g.N_q) {
         float f[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]) * mul;
+        for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[ch][e]) * mul;
         if constexpr (MODE == ROW_PREDO) {
-          // g_dO = g_dO' - dot2 * O  (P V = O)
-          const T* orow = (const T*)t.O + elem0 + ch * 16;
-          const uint4 o0 = reinterpret_cast<const uint4*>(orow)[0], o1 = reinterpret_cast<const uint4*>(orow)[1];
+          const uint4 o0 = o_[2 * ch], o1 = o_[2 * ch + 1];
           const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
@@ -544,6 +605,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) ROW_TRACE(0, 13);
   if (warp == kRowMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
