@@ -171,7 +171,7 @@ static EncodeTiledFn get_encode_fn() {
 static thread_local char tl_encode_error[160] = "";
 
 static bool encode_map(CUtensorMap* map, const void* ptr, int is_bf16, long long planes, long long rows,
-                       long long cols) {
+                       long long cols, int box_rows = 64) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     snprintf(tl_encode_error, sizeof(tl_encode_error), "driver entry point cuTensorMapEncodeTiled not found");
@@ -179,7 +179,7 @@ static bool encode_map(CUtensorMap* map, const void* ptr, int is_bf16, long long
   }
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
   cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * (cuuint64_t)cols * 2};
-  cuuint32_t box[3] = {64, 64, 1};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -191,7 +191,7 @@ static bool encode_map(CUtensorMap* map, const void* ptr, int is_bf16, long long
   return r == CUDA_SUCCESS;
 }
 
-bool encode_all_maps(TmaMaps* maps, const Geometry& g, const Tensors& t, int is_bf16, const char** err) {
+bool encode_all_maps(TmaMaps* maps, int op, const Geometry& g, const Tensors& t, int is_bf16, const char** err) {
   memset(maps, 0, sizeof(*maps));
   const void* ptrs[T_COUNT] = {t.Q, t.K, t.V, t.dO, t.g_dQ, t.g_dK, t.g_dV};
   const int rows[T_COUNT] = {g.N_q, g.N_kv, g.N_kv, g.N_q, g.N_q, g.N_kv, g.N_kv};
@@ -199,6 +199,25 @@ bool encode_all_maps(TmaMaps* maps, const Geometry& g, const Tensors& t, int is_
     const void* p = ptrs[i] ? ptrs[i] : t.Q;   // unused maps still need a valid encoding
     const int r = ptrs[i] ? rows[i] : g.N_q;
     if (!encode_map(&maps->m[i], p, is_bf16, g.BH, r, g.D)) {
+      *err = tl_encode_error;
+      return false;
+    }
+  }
+  // outputs of this operation, stored by TMA in boxes of 64 columns x 128 rows
+  void* outs[TO_COUNT] = {nullptr, nullptr, nullptr, nullptr};
+  int out_rows[TO_COUNT] = {g.N_q, g.N_q, g.N_kv, g.N_kv};
+  if (op == OP_FORWARD) {
+    outs[TO_O] = t.out_O;
+  } else if (op == OP_BACKWARD) {
+    outs[TO_dQ] = t.out_dQ; outs[TO_dK] = t.out_dK; outs[TO_dV] = t.out_dV;
+    out_rows[TO_dK] = g.N_kv; out_rows[TO_dV] = g.N_kv;
+  } else {
+    outs[TO_gdO] = t.out_g_dO; outs[TO_gQ] = t.out_g_Q; outs[TO_gK] = t.out_g_K; outs[TO_gV] = t.out_g_V;
+  }
+  for (int i = 0; i < TO_COUNT; ++i) {
+    void* p = outs[i] ? outs[i] : const_cast<void*>(t.Q);
+    const int r = outs[i] ? out_rows[i] : g.N_q;
+    if (!encode_map(&maps->out[i], p, is_bf16, g.BH, r, g.D, 128)) {
       *err = tl_encode_error;
       return false;
     }
@@ -255,7 +274,7 @@ cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cu
   *err = nullptr;
   TmaMaps maps;
   const int bf = dtype == 1;
-  if (!encode_all_maps(&maps, g, t, bf, err)) return cudaErrorInvalidValue;
+  if (!encode_all_maps(&maps, op, g, t, bf, err)) return cudaErrorInvalidValue;
   return bf ? launch_op<__nv_bfloat16>(op, maps, g, t, s, launches, phases)
             : launch_op<__half>(op, maps, g, t, s, launches, phases);
 }

@@ -455,37 +455,47 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after_sync();
     constexpr int kColsPerHalf = D / 2;
+    constexpr int kChunks = kColsPerHalf / 16;
+    // Both result tiles go out through the shared memory of the stationary operands (every
+    // product has completed): g_K over the K tile, g_V over the V tile.
 #pragma unroll
     for (int o = 0; o < 2; ++o) {
-      T* dst = (T*)(o == 0 ? t.out_g_K : t.out_g_V);
       const float mul = (o == 0) ? g.scale : 1.f;
-      // D is the padded head dimension of the tiles; the tensors in global memory have g.D columns
-      T* prow = dst + ((size_t)bh * g.N_kv + gidx) * g.D + half * kColsPerHalf;
+      const uint32_t tile = stat_base + (uint32_t)o * kAtoms * kAtomBytesStat;
+      uint32_t v[kChunks][16];
 #pragma unroll
-      for (int ch = 0; ch < kColsPerHalf / 16; ++ch) {
-        if (half * kColsPerHalf + ch * 16 >= g.D) break;   // padding columns (uniform over the warp)
-        uint32_t v[16];
+      for (int ch = 0; ch < kChunks; ++ch) {
         if (n_iter > 0 && ok) {
-          tmem_ld16(lane_addr + (o == 0 ? CF::kOut0 : CF::kOut1) + half * kColsPerHalf + ch * 16, v);
-          tmem_ld_wait(v);
+          tmem_ld16(lane_addr + (o == 0 ? CF::kOut0 : CF::kOut1) + half * kColsPerHalf + ch * 16, v[ch]);
         } else {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = 0u;
-        }
-        if (gidx < g.N_kv) {
-          uint4 w0, w1;
-          w0.x = Pack<T>::pack(__uint_as_float(v[0]) * mul, __uint_as_float(v[1]) * mul);
-          w0.y = Pack<T>::pack(__uint_as_float(v[2]) * mul, __uint_as_float(v[3]) * mul);
-          w0.z = Pack<T>::pack(__uint_as_float(v[4]) * mul, __uint_as_float(v[5]) * mul);
-          w0.w = Pack<T>::pack(__uint_as_float(v[6]) * mul, __uint_as_float(v[7]) * mul);
-          w1.x = Pack<T>::pack(__uint_as_float(v[8]) * mul, __uint_as_float(v[9]) * mul);
-          w1.y = Pack<T>::pack(__uint_as_float(v[10]) * mul, __uint_as_float(v[11]) * mul);
-          w1.z = Pack<T>::pack(__uint_as_float(v[12]) * mul, __uint_as_float(v[13]) * mul);
-          w1.w = Pack<T>::pack(__uint_as_float(v[14]) * mul, __uint_as_float(v[15]) * mul);
-          reinterpret_cast<uint4*>(prow + ch * 16)[0] = w0;
-          reinterpret_cast<uint4*>(prow + ch * 16)[1] = w1;
+          for (int e = 0; e < 16; ++e) v[ch][e] = 0u;
         }
       }
+      if (n_iter > 0 && ok) {
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch) tmem_ld_wait(v[ch]);
+      }
+#pragma unroll
+      for (int ch = 0; ch < kChunks; ++ch) {
+        const int col = half * kColsPerHalf + ch * 16;
+        if (col >= g.D) break;   // padding columns (uniform over the warp)
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          w[e] = Pack<T>::pack(__uint_as_float(v[ch][2 * e]) * mul, __uint_as_float(v[ch][2 * e + 1]) * mul);
+        store_op16(tile + (uint32_t)(col >> 6) * kAtomBytesStat, row, col & 63, w);
+      }
+    }
+    fence_proxy_async_smem();
+    named_barrier_sync(2, kMathWarps * 32);
+    if (threadIdx.x == 0) {
+      for (int o = 0; o < 2; ++o)
+        for (int a = 0; a * 64 < g.D; ++a)
+          tma_store_3d(&maps.out[o == 0 ? TO_gK : TO_gV], stat_base + (uint32_t)(o * kAtoms + a) * kAtomBytesStat,
+                       a * 64, r0, bh);
+      bulk_commit_group();
+      bulk_wait_group_read_all();
     }
   }
 

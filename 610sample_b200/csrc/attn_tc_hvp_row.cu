@@ -394,6 +394,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     if (n_iter > 0) {
       ok = mbar_wait(bar_staging_full, 0, abort_flag, t.status, wait_code(KIND, 12));
       ok = __all_sync(0xffffffffu, ok);
+      if (threadIdx.x == 0) ROW_TRACE(0, 14);
       if (ok) {
         constexpr int kChunksPerHalf = D / 16;    // 16-byte chunks (8 halves) of this thread's half row
 #pragma unroll
@@ -540,7 +541,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     }
     constexpr int kColsPerHalf = D / 2;
     constexpr int kChunks = kColsPerHalf / 16;
-    T* dst = (T*)(MODE == ROW_PREDO ? t.out_g_dO : t.out_g_Q);
     const float mul = (MODE == ROW_PREDO) ? 1.f : g.scale;
     // D is the padded head dimension of the tiles; the tensors in global memory have g.D columns
     const size_t elem0 = ((size_t)bh * g.N_q + gidx) * g.D + half * kColsPerHalf;
@@ -592,17 +592,18 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
             f[2 * e + 1] = fmaf(-dot2_row, of.y, f[2 * e + 1]);
           }
         }
-        uint4 w0, w1;
-        w0.x = Pack<T>::pack(f[0], f[1]);   w0.y = Pack<T>::pack(f[2], f[3]);
-        w0.z = Pack<T>::pack(f[4], f[5]);   w0.w = Pack<T>::pack(f[6], f[7]);
-        w1.x = Pack<T>::pack(f[8], f[9]);   w1.y = Pack<T>::pack(f[10], f[11]);
-        w1.z = Pack<T>::pack(f[12], f[13]); w1.w = Pack<T>::pack(f[14], f[15]);
-        reinterpret_cast<uint4*>(dst + elem0 + ch * 16)[0] = w0;
-        reinterpret_cast<uint4*>(dst + elem0 + ch * 16)[1] = w1;
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = Pack<T>::pack(f[2 * e], f[2 * e + 1]);
+        const int col = half * kColsPerHalf + ch * 16;
+        store_op16(strm_base + (uint32_t)(col >> 6) * kAtomBytesStat, row, col & 63, w);
       }
     }
+    // the result tile goes out through the first stream stage (every product has completed)
+    store_tile_tma(&maps.out[MODE == ROW_PREDO ? TO_gdO : TO_gQ], strm_base, g.D, r0, bh, threadIdx.x == 0);
   }
 
+  if (threadIdx.x == 0) ROW_TRACE(0, 15);
   tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) ROW_TRACE(0, 13);

@@ -23,7 +23,11 @@ constexpr uint32_t kOpTileBytes = BM * 128;     // [128 rows][64 halves], 16 KB
 enum Kind { FWD_LSE = 0, FWD_OUT, BWD_ROW, BWD_COL, HVP_PRE, HVP_ROW, HVP_COL };
 enum TensorId { T_Q = 0, T_K, T_V, T_dO, T_gQ, T_gK, T_gV, T_COUNT };
 
-struct TmaMaps { CUtensorMap m[T_COUNT]; };
+// Output tensors by operation: forward {O}; backward {dQ, dK, dV}; double backward
+// {g_dO, g_Q, g_K, g_V}.  Output maps have a box of 64 columns x 128 rows.
+enum OutId { TO_O = 0, TO_dQ = 0, TO_dK = 1, TO_dV = 2, TO_gdO = 0, TO_gQ = 1, TO_gK = 2, TO_gV = 3, TO_COUNT = 4 };
+
+struct TmaMaps { CUtensorMap m[T_COUNT]; CUtensorMap out[TO_COUNT]; };
 
 // Shared-memory control block (lives in the aux area).
 struct Control {
@@ -85,6 +89,21 @@ __device__ __forceinline__ void store_op16(uint32_t tile, int row, int col0, con
 }
 
 
+// Epilogue of the tensor-core kernels.  The 256 math threads have written a [128 rows][cols]
+// half-precision result tile to shared memory at `tile`, one 128-byte-swizzled 16 KB atom per 64
+// columns (store_op16).  All of them call this; `leader` (one thread) then writes the tile to
+// rows [row0, row0 + 128) of plane `plane` with one TMA store per atom (rows and columns beyond
+// the tensor are clipped by the map) and returns once shared memory has been read.
+__device__ __forceinline__ void store_tile_tma(const CUtensorMap* map, uint32_t tile, int cols, int row0, int plane,
+                                               bool leader) {
+  fence_proxy_async_smem();
+  named_barrier_sync(2, kMathWarps * 32);
+  if (leader) {
+    for (int a = 0; a * 64 < cols; ++a) tma_store_3d(map, tile + (uint32_t)a * kAtomBytesStat, a * 64, row0, plane);
+    bulk_commit_group();
+    bulk_wait_group_read_all();
+  }
+}
 
 }  // namespace tc
 }  // namespace attn
