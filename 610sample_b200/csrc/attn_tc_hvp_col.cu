@@ -26,7 +26,7 @@ namespace attn {
 namespace tc {
 
 constexpr int kColMmaWarp = 9;
-constexpr int kColThreads = 320;
+constexpr int kColThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
 
 struct ColControl {
   uint64_t stat_full;
@@ -188,7 +188,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   // =========================================================================
   // MMA issuer (converged warp, one elected lane issues)
   // =========================================================================
-  else if (warp == kColMmaWarp) {
+  else if (warp == kColMmaWarp || warp == kColMmaWarp + 1) {
     if (n_iter > 0) {
       bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
       ok = __all_sync(0xffffffffu, ok);
@@ -270,54 +270,50 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         __syncwarp();
       };
 
+      // Two issuing warps, so that the latency of one warp's waits falls while the products of the
+      // other are queued.  The tensor pipe needs no order between the two streams: RA(j+1) only
+      // waits for RA(j) to have been read, and RB(j+1) follows OUT(j), which reads RB, in the
+      // second warp's own order.
       auto wait_stream = [&](int tile) {
-        bool w = mbar_wait(bar_stream_full(tile & 1), (tile >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
-        w = __all_sync(0xffffffffu, w);
-        tc_fence_after_sync();
-        return w;
+        return mbar_wait(bar_stream_full(tile & 1), (tile >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
       };
-      auto wait_ra_free = [&](int tile) {    // the math warps have read RA of `tile`
-        bool w = mbar_wait(bar_ra_free, tile & 1, abort_flag, t.status, wait_code(KIND, 4));
-        w = __all_sync(0xffffffffu, w);
-        tc_fence_after_sync();
-        return w;
-      };
-      // Order per tile j: wait stream(j+1) [RA(j+1) head] wait op_full(j) [RA(j+1) tail] [OUT(j)]
-      // [RB(j+1) head] wait ra_free(j+1) [RB(j+1) tail].  RB(j+1) follows OUT(j), which reads RB,
-      // in the pipe's order.  With two stream stages tile j+2 is only requested once OUT(j) has
-      // completed, so the wait for it stays at the top of the next iteration.
-      ok = ok && wait_stream(0);
-      if (ok) {
-        issue_ra_head(strm_base); issue_ra_tail(strm_base);
-        issue_rb_head(strm_base); issue_rb_tail(strm_base);
-        if (n_iter > 1) ok = wait_ra_free(0);
-      }
-      for (int j = 0; j < n_iter && ok; ++j) {
-        const int st = j & 1, nst = st ^ 1;
-        const bool more = j + 1 < n_iter;
-        const uint32_t nstage = strm_base + nst * CF::kStageBytes;
-        if (more) {
-          ok = wait_stream(j + 1);
+      if (warp == kColMmaWarp) {
+        // ---- first warp: the RA products of every tile
+        for (int j = 0; j < n_iter && ok; ++j) {
+          ok = wait_stream(j);
+          if (ok && j > 0) ok = mbar_wait(bar_ra_free, (j - 1) & 1, abort_flag, t.status, wait_code(KIND, 4));
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          issue_ra_head(nstage);
+          tc_fence_after_sync();
+          const uint32_t stage = strm_base + (j & 1) * CF::kStageBytes;
+          issue_ra_head(stage);
+          issue_ra_tail(stage);
         }
-        ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
+      } else {
+        // ---- second warp: RB products and outputs
+        ok = ok && wait_stream(0);
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (more) issue_ra_tail(nstage);
-        issue_out(strm_base + st * CF::kStageBytes, j == 0);
-        commit(bar_stream_empty(st));
-        if (more) {
-          issue_rb_head(nstage);
-          if (j + 2 < n_iter) {
-            ok = wait_ra_free(j + 1);
-            if (!ok) break;
-          }
-          issue_rb_tail(nstage);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_rb_head(strm_base); issue_rb_tail(strm_base);
         }
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int st = j & 1, nst = st ^ 1;
+          const bool more = j + 1 < n_iter;
+          ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
+          if (ok && more) ok = wait_stream(j + 1);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_out(strm_base + st * CF::kStageBytes, j == 0);
+          commit(bar_stream_empty(st));
+          if (more) {
+            const uint32_t nstage = strm_base + nst * CF::kStageBytes;
+            issue_rb_head(nstage); issue_rb_tail(nstage);
+            }
+        }
+        if (ok) commit(bar_acc_done);
       }
-      if (ok) commit(bar_acc_done);
     }
   }
   // =========================================================================
@@ -340,29 +336,35 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
     float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2
     bool ok = true;
+    // Per-query scalars of a streamed tile, negated so that every use is a packed add / fma:
+    // [-L*log2(e) | -dot2 | -Dv | -(dot2*Dv + dot3)] x 64 queries; beyond N_q: -inf, 0, 0, 0 (p = 0).
+    // Thread (which, c) fetches one of them; the values of tile it+1 are fetched during tile it and
+    // published at its end, so that neither the global loads nor the hand-over are waited for.
+    const int which = threadIdx.x >> 6, qc = threadIdx.x & 63;
+    auto fetch_stat = [&](int tile_it) {
+      const int qi = (t_begin + tile_it) * BN + qc;
+      float v = (which == 0) ? -INFINITY : 0.f;
+      if (tile_it < n_iter && qi < g.N_q) {
+        if (which == 0) v = -__ldg(t.L + row_off + qi) * kLog2e;
+        else if (which == 1) v = -__ldg(t.dot2 + row_off + qi);
+        else if (which == 2) v = -__ldg(t.Dv + row_off + qi);
+        else v = -fmaf(__ldg(t.dot2 + row_off + qi), __ldg(t.Dv + row_off + qi), __ldg(t.dot3 + row_off + qi));
+      }
+      return v;
+    };
+    auto publish_stat = [&](int tile_it, float v) {
+      col_stats[(tile_it & 1) * 256 + which * 64 + qc] = v;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->stats_ready[tile_it & 1]));
+    };
+    if (n_iter > 0) publish_stat(0, fetch_stat(0));
     for (int it = 0; it < n_iter; ++it) {
       const int j0 = (t_begin + it) * BN;
-      // per-query scalars of the streamed tile, negated so that every use is a packed add / fma:
-      // [-L*log2(e) | -dot2 | -Dv | -(dot2*Dv + dot3)] x 64 queries; beyond N_q: -inf, 0, 0, 0 (p = 0)
       const float* cs = col_stats + (it & 1) * 256;
-      {
-        const int which = threadIdx.x >> 6, c = threadIdx.x & 63;
-        const int qi = j0 + c;
-        float v = (which == 0) ? -INFINITY : 0.f;
-        if (qi < g.N_q) {
-          if (which == 0) v = -t.L[row_off + qi] * kLog2e;
-          else if (which == 1) v = -t.dot2[row_off + qi];
-          else if (which == 2) v = -t.Dv[row_off + qi];
-          else v = -fmaf(t.dot2[row_off + qi], t.Dv[row_off + qi], t.dot3[row_off + qi]);
-        }
-        col_stats[(it & 1) * 256 + which * 64 + c] = v;
-        __syncwarp();
-        const uint32_t bar = smem_u32(&ctl->stats_ready[it & 1]);
-        if (lane == 0) mbar_arrive(bar);
-        ok = mbar_wait(bar, (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 9));
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
+      const float next_stat = fetch_stat(it + 1);
+      ok = mbar_wait(smem_u32(&ctl->stats_ready[it & 1]), (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 9));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       const int first = j0 + half * 32;
       const bool masked = !(first >= vlo && first + 31 < vhi);
 
@@ -448,6 +450,9 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_op_full);
+      // every warp has finished the previous tile (its operands were consumed before this tile's
+      // RB products were queued), so the other scalar buffer is free
+      if (it + 1 < n_iter) publish_stat(it + 1, next_stat);
     }
 
     // ---------------- outputs --------------------------------------------------------

@@ -42,13 +42,13 @@ enum RowMode { ROW_PREDO = 0, ROW_Q = 1 };
 
 // Experiment builds record clock stamps of CTA 0: slot = tile * 16 + event.
 #ifdef ATTN_EXPERIMENT
-#define ROW_TRACE(tile_, ev_) do { if (t.trace != nullptr && blockIdx.x == (unsigned)g.debug && (tile_) < 64) t.trace[(tile_) * 16 + (ev_)] = clock64(); } while (0)
+#define ROW_TRACE(tile_, ev_) do { if (tracing && ((tile_) >> 4) == 2) strace[(ev_) * 16 + ((tile_) & 15)] = (uint32_t)clock(); } while (0)
 #else
 #define ROW_TRACE(tile_, ev_) do { } while (0)
 #endif
 
 constexpr int kRowMmaWarp = 9;
-constexpr int kRowThreads = 320;
+constexpr int kRowThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
 
 constexpr int kRowStages = 3;
 
@@ -63,6 +63,7 @@ struct RowControl {
   uint64_t rb_full;
   uint64_t op_full;
   uint64_t acc_done;
+  uint64_t rb_issued;          // second issuing warp -> first: the RB products of a tile are queued
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
@@ -74,7 +75,11 @@ struct RowCfg {
   static constexpr uint32_t kStatBytes = kAtoms * kAtomBytesStat;            // g_dQ only
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
   static_assert(kStageBytes == 2 * kAtoms * kAtomBytesStat, "Q and dO are staged in one stream stage");
+#ifdef ATTN_EXPERIMENT
+  static constexpr uint32_t kAuxBytes = 256 + 1024;   // control block; clock stamps
+#else
   static constexpr uint32_t kAuxBytes = 256;          // control block
+#endif
   static constexpr uint32_t kContentBytes = kStatBytes + kRowStages * kStageBytes + kAuxBytes;
   static constexpr uint32_t kMaxSmem = 232448;
   static_assert(kContentBytes <= kMaxSmem, "shared memory over-subscribed");
@@ -115,12 +120,19 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t aux_off = CF::kStatBytes + kRowStages * CF::kStageBytes;
   const uint32_t staging = strm_base + 2 * CF::kStageBytes;   // Q then dO, before the third stage is used
   RowControl* ctl = reinterpret_cast<RowControl*>(smem_gen + aux_off);
+#ifdef ATTN_EXPERIMENT
+  volatile uint32_t* strace = reinterpret_cast<volatile uint32_t*>(smem_gen + aux_off + 256);
+  const bool tracing = t.trace != nullptr && blockIdx.x == (unsigned)g.debug;
+#endif
   // [2 halves][4][128] floats of row sums, exchanged after the last product has read the
   // g_dQ tile: its shared memory is reused
   float* row_sums = reinterpret_cast<float*>(smem_gen);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) ROW_TRACE(0, 10);
+#ifdef ATTN_EXPERIMENT
+  const long long t_entry = clock64();
+#endif
   const int tiles = (g.N_q + BM - 1) / BM;
   int bh, rank;
   cta_to_head_and_rank(g, tiles, bh, rank);
@@ -138,6 +150,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t bar_ra_full = smem_u32(&ctl->ra_full), bar_ra_free = smem_u32(&ctl->ra_free);
   const uint32_t bar_rb_full = smem_u32(&ctl->rb_full);
   const uint32_t bar_op_full = smem_u32(&ctl->op_full), bar_acc_done = smem_u32(&ctl->acc_done);
+  const uint32_t bar_rb_issued = smem_u32(&ctl->rb_issued);
   auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
   auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
 
@@ -154,6 +167,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     mbar_init(bar_rb_full, 1);
     mbar_init(bar_op_full, kMathWarps);
     mbar_init(bar_acc_done, 1);
+    mbar_init(bar_rb_issued, 1);
     ctl->abort_flag = 0u;
     ctl->tmem_base = 0u;
     fence_barrier_init();
@@ -206,6 +220,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         // the third stage doubles as the staging buffer of Q and dO until they are in tensor memory
         if (ok && it == 2) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 10));
         if (!ok) break;
+        if (it > 0) ROW_TRACE(it, 10);
         mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
         const uint32_t stage = strm_base + st * CF::kStageBytes;
 #pragma unroll
@@ -213,7 +228,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
             tma_load_3d(stage + CF::stream_off(s, a), &maps.m[CF::stream_tensor(s)], a * 64,
-                        (t_begin + it) * BN, bh, bar_stream_full(st));
+                        (t_begin + (g.debug == -3 ? 0 : it)) * BN, g.debug == -3 ? 0 : bh, bar_stream_full(st));
       }
       if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
         const long long t0 = clock64();
@@ -224,7 +239,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   // =========================================================================
   // MMA issuers (converged warps, one elected lane issues)
   // =========================================================================
-  else if (warp == kRowMmaWarp) {
+  else if (warp == kRowMmaWarp || warp == kRowMmaWarp + 1) {
     if (n_iter > 0) {
       bool ok = mbar_wait(bar_stat_full, 0, abort_flag, t.status, wait_code(KIND, 2));
       if (ok) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 11));
@@ -305,54 +320,61 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         __syncwarp();
       };
 
-      // wait for the streamed tile `tile` and for the math warps to have read RA of tile - 1
-      auto wait_for_ra = [&](int tile) {
-        bool w = mbar_wait(bar_stream_full(tile % kRowStages), (tile / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
-        if (w && tile > 0) w = mbar_wait(bar_ra_free, (tile - 1) & 1, abort_flag, t.status, wait_code(KIND, 4));
-        w = __all_sync(0xffffffffu, w);
-        tc_fence_after_sync();
-        return w;
+      // Two issuing warps, so that the latency of one warp's waits falls while the products of the
+      // other are queued.  The tensor pipe needs no order between the two streams: RA(j+1) only
+      // waits for RA(j) to have been read, and RB(j+1) follows OUT(j), which reads RB, in the
+      // second warp's own order.
+      auto wait_stream = [&](int tile) {
+        return mbar_wait(bar_stream_full(tile % kRowStages), (tile / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
       };
-      // Order per tile j: [RA(j+1) head] wait op_full(j) [RA(j+1) tail] [OUT(j)] [RB(j+1) head]
-      // wait stream(j+2), ra_free(j+1) [RB(j+1) tail].  RB(j+1) follows OUT(j), which reads RB, in
-      // the pipe's order.
-      ok = ok && wait_for_ra(0);
-      if (ok) {
-        issue_ra_head(strm_base, 0); issue_ra_tail(strm_base);
-        issue_rb_head(strm_base); issue_rb_tail(strm_base);
-        if (n_iter > 1) ok = wait_for_ra(1);
-      }
-      for (int j = 0; j < n_iter && ok; ++j) {
-        const int st = j % kRowStages, nst = (j + 1) % kRowStages;
-        const bool more = j + 1 < n_iter;
-        const uint32_t nstage = strm_base + nst * CF::kStageBytes;
-        if (more) {
-          if (lane == 0) ROW_TRACE(j + 1, 0);
-          issue_ra_head(nstage, j + 1);
+      if (warp == kRowMmaWarp) {
+        // ---- first warp: the RA products of every tile
+        for (int j = 0; j < n_iter && ok; ++j) {
+          ok = wait_stream(j);
+          if (ok && j > 0) ok = mbar_wait(bar_ra_free, (j - 1) & 1, abort_flag, t.status, wait_code(KIND, 4));
+          // ROW_Q keeps the pipe's order OUT(j-2), RB(j-1), RA(j): its second half-step is the long
+          // one, and RA(j) queued any earlier delays the outputs that half-step waits behind.  The
+          // scalar pass is faster with the two streams left to run freely (both measured).
+          if (MODE == ROW_Q && ok && j > 0) ok = mbar_wait(bar_rb_issued, (j - 1) & 1, abort_flag, t.status, wait_code(KIND, 13));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t stage = strm_base + (j % kRowStages) * CF::kStageBytes;
+          if (lane == 0) ROW_TRACE(j, 0);
+          issue_ra_head(stage, j);
+          issue_ra_tail(stage);
+          if (lane == 0) ROW_TRACE(j, 1);
         }
-        ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
+      } else {
+        // ---- second warp: RB products and outputs
+        ok = ok && wait_stream(0);
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (more) {
-          issue_ra_tail(nstage);
-          if (lane == 0) ROW_TRACE(j + 1, 1);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_rb_head(strm_base); issue_rb_tail(strm_base);
+          if (lane == 0) mbar_arrive(bar_rb_issued);
         }
-        if (lane == 0) ROW_TRACE(j, 4);
-        issue_out(strm_base + st * CF::kStageBytes, j == 0);
-        commit(bar_stream_empty(st));
-        if (lane == 0) ROW_TRACE(j, 5);
-        if (more) {
-          issue_rb_head(nstage);
-          if (j + 2 < n_iter) {
-            ok = wait_for_ra(j + 2);
-            if (!ok) break;
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int st = j % kRowStages, nst = (j + 1) % kRowStages;
+          const bool more = j + 1 < n_iter;
+          ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
+          if (ok && more) ok = wait_stream(j + 1);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (lane == 0) ROW_TRACE(j, 4);
+          issue_out(strm_base + st * CF::kStageBytes, j == 0);
+          commit(bar_stream_empty(st));
+          if (lane == 0) ROW_TRACE(j, 5);
+          if (more) {
+            const uint32_t nstage = strm_base + nst * CF::kStageBytes;
+            issue_rb_head(nstage); issue_rb_tail(nstage);
+            if (lane == 0) mbar_arrive(bar_rb_issued);
+            if (lane == 0) ROW_TRACE(j + 1, 3);
           }
-          issue_rb_tail(nstage);
-          if (lane == 0) ROW_TRACE(j + 1, 3);
         }
+        if (ok) commit(bar_acc_done);
       }
-      if (ok) commit(bar_acc_done);
     }
   }
   // =========================================================================
@@ -607,6 +629,17 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) ROW_TRACE(0, 13);
+#ifdef ATTN_EXPERIMENT
+  if (tracing && threadIdx.x < 256) t.trace[threadIdx.x] = strace[threadIdx.x];
+  if (threadIdx.x == 0 && t.trace != nullptr && g.debug <= -1 && blockIdx.x < 4096) {   // per-CTA record
+    unsigned smid;
+    asm("mov.u32 %0, %%smid;" : "=r"(smid));
+    t.trace[1024 + blockIdx.x * 4 + 0] = n_iter;
+    t.trace[1024 + blockIdx.x * 4 + 1] = clock64() - t_entry;
+    t.trace[1024 + blockIdx.x * 4 + 2] = smid;
+    t.trace[1024 + blockIdx.x * 4 + 3] = t_entry;
+  }
+#endif
   if (warp == kRowMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
