@@ -26,14 +26,23 @@ namespace attn {
 namespace tc {
 
 constexpr int kColMmaWarp = 9;
+
+// Experiment builds keep clock stamps of tiles 36 and 37 of one CTA in the spare bytes of the control block.
+#ifdef ATTN_EXPERIMENT
+#define COL_TRACE(tile_, ev_) do { if (tracing && ((tile_) >> 1) == 18) strace[(ev_) * 2 + ((tile_) & 1)] = (uint32_t)clock(); } while (0)
+#else
+#define COL_TRACE(tile_, ev_) do { } while (0)
+#endif
 constexpr int kColThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
 
 struct ColControl {
   uint64_t stat_full;
-  uint64_t stream_full[2];
+  uint64_t stream_full[2];     // Q and g_dQ of a streamed tile have landed
+  uint64_t stream_full_do[2];  // its dO has landed
   uint64_t stream_empty[2];
   uint64_t ra_full, ra_free;
   uint64_t rb_full;
+  uint64_t op_half;            // operands of the even k-steps (first 16 queries of each half) written
   uint64_t op_full;
   uint64_t acc_done;
   uint64_t stats_ready[2];
@@ -93,6 +102,11 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t aux_off = CF::kStatBytes + 2 * CF::kStageBytes;
   ColControl* ctl = reinterpret_cast<ColControl*>(smem_gen + aux_off);
   float* col_stats = reinterpret_cast<float*>(smem_gen + aux_off + 256);   // [2][4][64]
+#ifdef ATTN_EXPERIMENT
+  volatile uint32_t* strace = reinterpret_cast<volatile uint32_t*>(smem_gen + aux_off + 144);
+  static_assert(sizeof(ColControl) <= 144, "clock stamps overlap the control block");
+  const bool tracing = t.trace != nullptr && blockIdx.x == (unsigned)g.debug;
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles = (g.N_kv + BM - 1) / BM;
@@ -109,13 +123,16 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t bar_ra_full = smem_u32(&ctl->ra_full), bar_ra_free = smem_u32(&ctl->ra_free);
   const uint32_t bar_rb_full = smem_u32(&ctl->rb_full);
   const uint32_t bar_op_full = smem_u32(&ctl->op_full), bar_acc_done = smem_u32(&ctl->acc_done);
+  const uint32_t bar_op_half = smem_u32(&ctl->op_half);
   auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
+  auto bar_stream_full_do = [&](int s) { return smem_u32(&ctl->stream_full_do[s]); };
   auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
 
   if (threadIdx.x == 0) {
     mbar_init(bar_stat_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_stream_full(s), 1);
+      mbar_init(bar_stream_full_do(s), 1);
       mbar_init(bar_stream_empty(s), 1);
       mbar_init(smem_u32(&ctl->stats_ready[s]), kMathWarps);
     }
@@ -123,6 +140,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     mbar_init(bar_ra_free, kMathWarps);
     mbar_init(bar_rb_full, 1);
     mbar_init(bar_op_full, kMathWarps);
+    mbar_init(bar_op_half, kMathWarps);
     mbar_init(bar_acc_done, 1);
     ctl->abort_flag = 0u;
     ctl->tmem_base = 0u;
@@ -134,7 +152,8 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   // allocation and the second barrier: their latency is the longest item of the prologue
   if (warp == kProducerWarp && lane == 0 && n_iter > 0) {
     mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
-    mbar_arrive_expect_tx(bar_stream_full(0), CF::kStageBytes);
+    mbar_arrive_expect_tx(bar_stream_full(0), 2 * kAtoms * kAtomBytesStrm);
+    mbar_arrive_expect_tx(bar_stream_full_do(0), kAtoms * kAtomBytesStrm);
 #pragma unroll
     for (int s = 0; s < CF::kNStat; ++s) {
 #pragma unroll
@@ -149,7 +168,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
             tma_load_3d(strm_base + CF::stream_off(sl, a), &maps.m[CF::stream_tensor(sl)], a * 64, t_begin * BN, bh,
-                        bar_stream_full(0));
+                        sl < 2 ? bar_stream_full(0) : bar_stream_full_do(0));
       }
     }
   }
@@ -170,14 +189,16 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         const int st = it & 1;
         ok = mbar_wait(bar_stream_empty(st), ((it >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
+        // Q and g_dQ first, on their own barrier: the RA products of the tile need only them
+        mbar_arrive_expect_tx(bar_stream_full(st), 2 * kAtoms * kAtomBytesStrm);
+        mbar_arrive_expect_tx(bar_stream_full_do(st), kAtoms * kAtomBytesStrm);
         const uint32_t stage = strm_base + st * CF::kStageBytes;
 #pragma unroll
         for (int s = 0; s < CF::kNStream; ++s)
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
             tma_load_3d(stage + CF::stream_off(s, a), &maps.m[CF::stream_tensor(s)], a * 64,
-                        (t_begin + it) * BN, bh, bar_stream_full(st));
+                        (t_begin + it) * BN, bh, s < 2 ? bar_stream_full(st) : bar_stream_full_do(st));
       }
       if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
         const long long t0 = clock64();
@@ -254,18 +275,21 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         }
         __syncwarp();
       };
-      auto issue_out = [&](uint32_t stage, bool first) {    // operands: dS^T at RB, g_dp^T at RB+16, g_S^T at RB+64
+      // The output products of one tile in two parts: the k-steps of parity `par` (the math warps
+      // write the operands of the even k-steps first and announce them on their own barrier).
+      // Operands: dS^T at RB, g_dp^T at RB+16, g_S^T at RB+64.
+      auto issue_out = [&](uint32_t stage, bool first, int par) {
         // the atoms of Q and g_dQ are interleaved, those of dO follow one another
         const uint64_t dm01 = smem_desc_sw128(stage, CF::stream_atom_stride(0), 1024);
         const uint64_t dm2 = smem_desc_sw128(stage, CF::stream_atom_stride(2), 1024);
         static_assert(CF::stream_atom_stride(0) == CF::stream_atom_stride(1), "Q and g_dQ share a layout");
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += dS^T g_dQ
-            mma_ts(out0, op_tmem(CF::kRB, ks), dm01 + moff(1, ks), idesc_out, !(first && ks == 0));
+            if ((ks & 1) == par) mma_ts(out0, op_tmem(CF::kRB, ks), dm01 + moff(1, ks), idesc_out, !(first && ks == 0));
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_K += g_S^T Q
-            mma_ts(out0, op_tmem(CF::kRB + 64, ks), dm01 + moff(0, ks), idesc_out, 1);
+            if ((ks & 1) == par) mma_ts(out0, op_tmem(CF::kRB + 64, ks), dm01 + moff(0, ks), idesc_out, 1);
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)   // g_V += g_dp^T dO
-            mma_ts(out1, op_tmem(CF::kRB + 16, ks), dm2 + moff(2, ks), idesc_out, !(first && ks == 0));
+            if ((ks & 1) == par) mma_ts(out1, op_tmem(CF::kRB + 16, ks), dm2 + moff(2, ks), idesc_out, !(first && ks == 0));
         }
         __syncwarp();
       };
@@ -274,8 +298,11 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       // other are queued.  The tensor pipe needs no order between the two streams: RA(j+1) only
       // waits for RA(j) to have been read, and RB(j+1) follows OUT(j), which reads RB, in the
       // second warp's own order.
-      auto wait_stream = [&](int tile) {
+      auto wait_stream = [&](int tile) {       // Q and g_dQ of the tile
         return mbar_wait(bar_stream_full(tile & 1), (tile >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
+      };
+      auto wait_stream_do = [&](int tile) {    // dO of the tile
+        return mbar_wait(bar_stream_full_do(tile & 1), (tile >> 1) & 1, abort_flag, t.status, wait_code(KIND, 13));
       };
       if (warp == kColMmaWarp) {
         // ---- first warp: the RA products of every tile
@@ -286,12 +313,14 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t stage = strm_base + (j & 1) * CF::kStageBytes;
+          if (lane == 0) COL_TRACE(j, 0);
           issue_ra_head(stage);
           issue_ra_tail(stage);
+          if (lane == 0) COL_TRACE(j, 1);
         }
       } else {
         // ---- second warp: RB products and outputs
-        ok = ok && wait_stream(0);
+        ok = ok && wait_stream_do(0);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
           tc_fence_after_sync();
@@ -300,13 +329,22 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         for (int j = 0; j < n_iter && ok; ++j) {
           const int st = j & 1, nst = st ^ 1;
           const bool more = j + 1 < n_iter;
-          ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
-          if (ok && more) ok = wait_stream(j + 1);
+          ok = mbar_wait(bar_op_half, j & 1, abort_flag, t.status, wait_code(KIND, 14));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_out(strm_base + st * CF::kStageBytes, j == 0);
+          if (lane == 0) COL_TRACE(j, 2);
+          issue_out(strm_base + st * CF::kStageBytes, j == 0, 0);
+          if (lane == 0) COL_TRACE(j, 3);
+          ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
+          if (ok && more) ok = wait_stream_do(j + 1);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (lane == 0) COL_TRACE(j, 4);
+          issue_out(strm_base + st * CF::kStageBytes, j == 0, 1);
           commit(bar_stream_empty(st));
+          if (lane == 0) COL_TRACE(j, 5);
           if (more) {
             const uint32_t nstage = strm_base + nst * CF::kStageBytes;
             issue_rb_head(nstage); issue_rb_tail(nstage);
@@ -365,6 +403,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       ok = mbar_wait(smem_u32(&ctl->stats_ready[it & 1]), (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 9));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (threadIdx.x == 0) COL_TRACE(it, 12);
       const int first = j0 + half * 32;
       const bool masked = !(first >= vlo && first + 31 < vhi);
 
@@ -373,6 +412,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 0) COL_TRACE(it, 6);
       {
         uint32_t s_[2][16], g_[2][16];
         tmem_ld16(ra + half * 32, s_[0]);
@@ -407,10 +447,12 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       }
 
       // ---------------- half-step 2: RB -> operands dS, g_dp, g_S ------------------
+      if (threadIdx.x == 0) COL_TRACE(it, 7);
       ok = mbar_wait(bar_rb_full, it & 1, abort_flag, t.status, wait_code(KIND, 7));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 0) COL_TRACE(it, 8);
       {
         uint32_t dp_[2][16], gp_[2][16];
         tmem_ld16(rb + half * 32, dp_[0]);
@@ -444,12 +486,20 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           tmem_st8(rb + half * 32 + ch * 8, kds);
           tmem_st8(rb + half * 32 + 16 + ch * 8, kgdp);
           tmem_st8(rb + 64 + half * 32 + ch * 8, kgs);
+          if (ch == 0) {     // the even k-steps of the output products can start
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_op_half);
+            if (threadIdx.x == 0) COL_TRACE(it, 11);
+          }
         }
       }
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_op_full);
+      if (threadIdx.x == 0) COL_TRACE(it, 9);
       // every warp has finished the previous tile (its operands were consumed before this tile's
       // RB products were queued), so the other scalar buffer is free
       if (it + 1 < n_iter) publish_stat(it + 1, next_stat);
@@ -506,6 +556,9 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
   tc_fence_before_sync();
   __syncthreads();
+#ifdef ATTN_EXPERIMENT
+  if (tracing && threadIdx.x < 28) t.trace[threadIdx.x] = strace[threadIdx.x];
+#endif
   if (warp == kColMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
