@@ -78,10 +78,6 @@ attn::Geometry make_geometry(const attn_shape_t* s) {
   g.window = s->window_size > (1 << 30) ? (1 << 30) : s->window_size;
   g.mask_mode = s->mask_mode;
   g.head_group = 1;
-  g.debug = 0;
-#ifdef ATTN_EXPERIMENT
-  if (const char* e = getenv("ATTN_B200_DEBUG")) g.debug = atoi(e);
-#endif
   g.scale = 1.0f / sqrtf((float)s->D);
   g.scale_log2e = g.scale * attn::kLog2e;
   return g;
@@ -130,9 +126,6 @@ int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream, int phase
   if (e0 != cudaSuccess) return fail(ATTN_ECUDA, "cudaFree(0): %s", cudaGetErrorString(e0));
   int rc = status_pointer(&t.status);
   if (rc != ATTN_OK) return rc;
-#ifdef ATTN_EXPERIMENT
-  if (const char* e = getenv("ATTN_B200_TRACE")) t.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
-#endif
   const bool use_tc = s->impl == ATTN_IMPL_TENSOR ||
                       (s->impl == ATTN_IMPL_AUTO && attn::tc_supported(s->dtype, s->D));
   cudaStream_t cs = static_cast<cudaStream_t>(stream);

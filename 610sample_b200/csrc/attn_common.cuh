@@ -30,7 +30,6 @@ struct Geometry {
   int ki_base;   // absolute index of key row 0    (= chunk_id * N_q + N_q - N_kv)
   int window;    // clamped to 2^30 so qi < ki + window never overflows
   int mask_mode; // 0 reference mask, 1 none
-  int debug;       // experiment switches; only read by builds with ATTN_EXPERIMENT defined
   // CTA order: heads are taken in groups of `head_group`; within a group the CTAs go tile by
   // tile, heavy tiles first, over all heads of the group.  Large groups balance the SMs (longest
   // work first), small groups keep the streamed tensors of the heads in flight inside the L2.
@@ -145,9 +144,6 @@ __device__ __forceinline__ void cta_to_head_and_rank(const Geometry& g, int tile
 // heads per group: as many as keep `streamed_bytes_per_head` of every head of the group within
 // about 16 MB of L2, all heads when the grid is small anyway
 inline int pick_head_group(long long ctas, int BH, long long streamed_bytes_per_head) {
-#ifdef ATTN_EXPERIMENT
-  if (const char* e = getenv("ATTN_B200_GROUP")) { int n = atoi(e); if (n >= 1) return n > BH ? BH : n; }
-#endif
   if (ctas < 8 * 148) return BH > 0 ? BH : 1;
   long long n = (16ll << 20) / (streamed_bytes_per_head > 0 ? streamed_bytes_per_head : 1);
   if (n < 1) n = 1;
@@ -161,7 +157,6 @@ struct Tensors {
   void *out_O, *out_dQ, *out_dK, *out_dV, *out_g_dO, *out_g_Q, *out_g_K, *out_g_V;
   float* out_L;
   float *Dv, *dot2, *dot3;                               // scratch, [BH, N_q] each
-  long long* trace;      // experiment builds only: per-event clock stamps of CTA 0 (else null)
   unsigned int* status;  // device status word: a kernel that gives up on a bounded
                          // wait stores a non-zero code here and returns
 };

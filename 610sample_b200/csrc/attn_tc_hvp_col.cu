@@ -13,11 +13,16 @@
 // half-precision operands dS = p (dP - Dv), g_dp = p a and g_S = p (a (dP - Dv) + gPdV - c3),
 // c3 = dot2 Dv + dot3, over the RB columns the thread has just read; the output products take
 // them from there (A operand in tensor memory), so no operand tile goes through shared memory
-// and the two column halves of a row never race.  The per-query scalars (L, Dv, dot2, c3) of the
-// streamed tile are staged in shared memory by the math warps themselves.
-// One warp issues every MMA in a fixed order per tile: RA products of the next tile (the math
-// warps wait for those first), output products of this tile, RB products of the next tile, so
-// RB is overwritten only after the outputs that read it.
+// and the two column halves of a row never race.  The per-query scalars (L, Dv, dot2, c3) of a
+// streamed tile are fetched by the math warps one tile ahead and handed over in shared memory.
+// Two warps issue the MMAs, each batch by one elected lane inside a single branch: the first warp
+// the RA products of every tile (they need only Q and g_dQ, which land on their own barrier), the
+// second the output products of a tile -- in two halves, the even k-steps as soon as their
+// operands are written -- followed by the RB products of the next tile, so RB is overwritten only
+// after the outputs that read it.  Shared memory holds 128 KB of stationary operands, so there is
+// room for two stream stages only: the load of tile j+2 starts when the outputs of tile j have
+// completed, and that latency is what the tensor pipe idles on in this kernel.
+// The two result tiles leave through shared memory and TMA stores.
 // Formulas: reference csrc/flash_double_backward_v7.cu:1583-1675.
 #include "attn_launch.h"
 #include "tc_common.cuh"
@@ -27,12 +32,6 @@ namespace tc {
 
 constexpr int kColMmaWarp = 9;
 
-// Experiment builds keep clock stamps of tiles 36 and 37 of one CTA in the spare bytes of the control block.
-#ifdef ATTN_EXPERIMENT
-#define COL_TRACE(tile_, ev_) do { if (tracing && ((tile_) >> 1) == 18) strace[(ev_) * 2 + ((tile_) & 1)] = (uint32_t)clock(); } while (0)
-#else
-#define COL_TRACE(tile_, ev_) do { } while (0)
-#endif
 constexpr int kColThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
 
 struct ColControl {
@@ -102,11 +101,6 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t aux_off = CF::kStatBytes + 2 * CF::kStageBytes;
   ColControl* ctl = reinterpret_cast<ColControl*>(smem_gen + aux_off);
   float* col_stats = reinterpret_cast<float*>(smem_gen + aux_off + 256);   // [2][4][64]
-#ifdef ATTN_EXPERIMENT
-  volatile uint32_t* strace = reinterpret_cast<volatile uint32_t*>(smem_gen + aux_off + 144);
-  static_assert(sizeof(ColControl) <= 144, "clock stamps overlap the control block");
-  const bool tracing = t.trace != nullptr && blockIdx.x == (unsigned)g.debug;
-#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles = (g.N_kv + BM - 1) / BM;
@@ -313,10 +307,8 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t stage = strm_base + (j & 1) * CF::kStageBytes;
-          if (lane == 0) COL_TRACE(j, 0);
           issue_ra_head(stage);
           issue_ra_tail(stage);
-          if (lane == 0) COL_TRACE(j, 1);
         }
       } else {
         // ---- second warp: RB products and outputs
@@ -333,18 +325,14 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          if (lane == 0) COL_TRACE(j, 2);
           issue_out(strm_base + st * CF::kStageBytes, j == 0, 0);
-          if (lane == 0) COL_TRACE(j, 3);
           ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 5));
           if (ok && more) ok = wait_stream_do(j + 1);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          if (lane == 0) COL_TRACE(j, 4);
           issue_out(strm_base + st * CF::kStageBytes, j == 0, 1);
           commit(bar_stream_empty(st));
-          if (lane == 0) COL_TRACE(j, 5);
           if (more) {
             const uint32_t nstage = strm_base + nst * CF::kStageBytes;
             issue_rb_head(nstage); issue_rb_tail(nstage);
@@ -403,7 +391,6 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       ok = mbar_wait(smem_u32(&ctl->stats_ready[it & 1]), (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 9));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (threadIdx.x == 0) COL_TRACE(it, 12);
       const int first = j0 + half * 32;
       const bool masked = !(first >= vlo && first + 31 < vhi);
 
@@ -412,7 +399,6 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if (threadIdx.x == 0) COL_TRACE(it, 6);
       {
         uint32_t s_[2][16], g_[2][16];
         tmem_ld16(ra + half * 32, s_[0]);
@@ -447,12 +433,10 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       }
 
       // ---------------- half-step 2: RB -> operands dS, g_dp, g_S ------------------
-      if (threadIdx.x == 0) COL_TRACE(it, 7);
       ok = mbar_wait(bar_rb_full, it & 1, abort_flag, t.status, wait_code(KIND, 7));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if (threadIdx.x == 0) COL_TRACE(it, 8);
       {
         uint32_t dp_[2][16], gp_[2][16];
         tmem_ld16(rb + half * 32, dp_[0]);
@@ -491,7 +475,6 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_op_half);
-            if (threadIdx.x == 0) COL_TRACE(it, 11);
           }
         }
       }
@@ -499,7 +482,6 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_op_full);
-      if (threadIdx.x == 0) COL_TRACE(it, 9);
       // every warp has finished the previous tile (its operands were consumed before this tile's
       // RB products were queued), so the other scalar buffer is free
       if (it + 1 < n_iter) publish_stat(it + 1, next_stat);
@@ -556,9 +538,6 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
   tc_fence_before_sync();
   __syncthreads();
-#ifdef ATTN_EXPERIMENT
-  if (tracing && threadIdx.x < 28) t.trace[threadIdx.x] = strace[threadIdx.x];
-#endif
   if (warp == kColMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);

@@ -1,10 +1,8 @@
 // Row-side kernels of the double backward (Hessian-vector product) on sm_100a.
 //
 // The query side of the HVP needs two [128 x D] fp32 accumulators (g_Q, g_dO).  At
-// D = 128 they would fill half of tensor memory and leave each score region
-// single-buffered, which chains every tensor-core product behind the math warps.
-// The work is therefore split over two kernels with ONE accumulator each, which
-// frees 128 columns to double-buffer the [S | gdS] region:
+// D = 128 they would fill half of tensor memory.  The work is therefore split over two
+// kernels with ONE accumulator each, which leaves 128 columns for the stationary operands:
 //
 //   ROW_PREDO  per-row scalars Dv, dot2, dot3 (to scratch) and
 //                g_dO = P g_dV + (P o gdS) V - dot2 o O
@@ -14,9 +12,9 @@
 //
 // Both stream K, g_dK, V, g_dV in 64-row tiles (three TMA stages) past 128 stationary
 // rows of Q, dO, g_dQ.  Q and dO are copied once into TENSOR MEMORY and used from there
-// as the A operand of their score products (a stationary operand in shared memory is
-// re-read by every MMA instruction, and shared-memory operand bandwidth is what limits
-// these kernels); g_dQ stays in shared memory.
+// as the A operand of their score products (an A operand in shared memory is re-read by
+// every MMA instruction: measured 48 instead of 32 clocks for an N = 64 product); g_dQ
+// stays in shared memory.
 // Tensor memory:  RA [0,128) = [S | gdS] = [Q K^T | Q g_dK^T + g_dQ K^T];
 // RB [128,256) = [dP | gPdV] = dO [V; g_dV]^T;  OUT [256,256+D);  Q at [384,384+D/2),
 // dO at [448,448+D/2) (two halves per 32-bit column).  Per tile the math warps run two
@@ -26,11 +24,12 @@
 //   half-step 2 reads RB:  ROW_PREDO accumulates Dv, A, E (dot3 = A - 2 Dv dot2 + E) and
 //               writes the operands P and P o gdS over RB; ROW_Q writes dS = p (dP - Dv) and
 //               g_S = p (a (dP - Dv) + gPdV - c3), c3 = dot2 Dv + dot3, over RB.
-// Output products take their A operand from RB.  One warp issues every MMA in a fixed order
-// per tile -- RA products of the next tile (the math warps wait for those first), outputs of
-// this tile, RB products of the next tile -- so RB is overwritten only after the outputs that
-// read it.  (Two issuing warps were measured slower here: the RB work lands on top of the RA
-// products that are on the critical path.)
+// Output products take their A operand from RB.  Two warps issue the MMAs, each batch by one
+// elected lane inside a single branch: the first warp the RA products of every tile, the second
+// the outputs of a tile followed by the RB products of the next (so RB is overwritten only after
+// the outputs that read it).  With one issuing warp the latency of each of its waits (about 150
+// clocks even when satisfied) fell on an empty tensor pipe.  The result tile leaves through
+// shared memory and a TMA store, which clips rows and columns beyond the tensor.
 // Formulas: reference csrc/flash_double_backward_v7.cu:1257-1454.
 #include "attn_launch.h"
 #include "tc_common.cuh"
@@ -39,13 +38,6 @@ namespace attn {
 namespace tc {
 
 enum RowMode { ROW_PREDO = 0, ROW_Q = 1 };
-
-// Experiment builds record clock stamps of CTA 0: slot = tile * 16 + event.
-#ifdef ATTN_EXPERIMENT
-#define ROW_TRACE(tile_, ev_) do { if (tracing && ((tile_) >> 4) == 2) strace[(ev_) * 16 + ((tile_) & 15)] = (uint32_t)clock(); } while (0)
-#else
-#define ROW_TRACE(tile_, ev_) do { } while (0)
-#endif
 
 constexpr int kRowMmaWarp = 9;
 constexpr int kRowThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
@@ -75,11 +67,7 @@ struct RowCfg {
   static constexpr uint32_t kStatBytes = kAtoms * kAtomBytesStat;            // g_dQ only
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
   static_assert(kStageBytes == 2 * kAtoms * kAtomBytesStat, "Q and dO are staged in one stream stage");
-#ifdef ATTN_EXPERIMENT
-  static constexpr uint32_t kAuxBytes = 256 + 1024;   // control block; clock stamps
-#else
   static constexpr uint32_t kAuxBytes = 256;          // control block
-#endif
   static constexpr uint32_t kContentBytes = kStatBytes + kRowStages * kStageBytes + kAuxBytes;
   static constexpr uint32_t kMaxSmem = 232448;
   static_assert(kContentBytes <= kMaxSmem, "shared memory over-subscribed");
@@ -120,19 +108,11 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t aux_off = CF::kStatBytes + kRowStages * CF::kStageBytes;
   const uint32_t staging = strm_base + 2 * CF::kStageBytes;   // Q then dO, before the third stage is used
   RowControl* ctl = reinterpret_cast<RowControl*>(smem_gen + aux_off);
-#ifdef ATTN_EXPERIMENT
-  volatile uint32_t* strace = reinterpret_cast<volatile uint32_t*>(smem_gen + aux_off + 256);
-  const bool tracing = t.trace != nullptr && blockIdx.x == (unsigned)g.debug;
-#endif
   // [2 halves][4][128] floats of row sums, exchanged after the last product has read the
   // g_dQ tile: its shared memory is reused
   float* row_sums = reinterpret_cast<float*>(smem_gen);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) ROW_TRACE(0, 10);
-#ifdef ATTN_EXPERIMENT
-  const long long t_entry = clock64();
-#endif
   const int tiles = (g.N_q + BM - 1) / BM;
   int bh, rank;
   cta_to_head_and_rank(g, tiles, bh, rank);
@@ -220,7 +200,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         // the third stage doubles as the staging buffer of Q and dO until they are in tensor memory
         if (ok && it == 2) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 10));
         if (!ok) break;
-        if (it > 0) ROW_TRACE(it, 10);
         mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
         const uint32_t stage = strm_base + st * CF::kStageBytes;
 #pragma unroll
@@ -228,7 +207,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
             tma_load_3d(stage + CF::stream_off(s, a), &maps.m[CF::stream_tensor(s)], a * 64,
-                        (t_begin + (g.debug == -3 ? 0 : it)) * BN, g.debug == -3 ? 0 : bh, bar_stream_full(st));
+                        (t_begin + it) * BN, bh, bar_stream_full(st));
       }
       if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
         const long long t0 = clock64();
@@ -275,7 +254,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
             if (ks < ks_n) mma_ts(ra, qt + 8 * ks, dk + koff(0, ks), kIdesc128, ks > 0);
-          ROW_TRACE(tr_tile, 2);
           _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)
             if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
         }
@@ -340,10 +318,8 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t stage = strm_base + (j % kRowStages) * CF::kStageBytes;
-          if (lane == 0) ROW_TRACE(j, 0);
           issue_ra_head(stage, j);
           issue_ra_tail(stage);
-          if (lane == 0) ROW_TRACE(j, 1);
         }
       } else {
         // ---- second warp: RB products and outputs
@@ -362,15 +338,12 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          if (lane == 0) ROW_TRACE(j, 4);
           issue_out(strm_base + st * CF::kStageBytes, j == 0);
           commit(bar_stream_empty(st));
-          if (lane == 0) ROW_TRACE(j, 5);
           if (more) {
             const uint32_t nstage = strm_base + nst * CF::kStageBytes;
             issue_rb_head(nstage); issue_rb_tail(nstage);
             if (lane == 0) mbar_arrive(bar_rb_issued);
-            if (lane == 0) ROW_TRACE(j + 1, 3);
           }
         }
         if (ok) commit(bar_acc_done);
@@ -416,7 +389,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     if (n_iter > 0) {
       ok = mbar_wait(bar_staging_full, 0, abort_flag, t.status, wait_code(KIND, 12));
       ok = __all_sync(0xffffffffu, ok);
-      if (threadIdx.x == 0) ROW_TRACE(0, 14);
       if (ok) {
         constexpr int kChunksPerHalf = D / 16;    // 16-byte chunks (8 halves) of this thread's half row
 #pragma unroll
@@ -442,7 +414,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_stat_tmem_ready);
-      if (threadIdx.x == 0) ROW_TRACE(0, 11);
     }
 
     float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2 (ROW_PREDO: a_ = p * gdS)
@@ -458,7 +429,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if (threadIdx.x == 0) ROW_TRACE(it, 6);
       // Read this thread's 2 x 32 columns of RA in one go and release the region before the
       // arithmetic: the next tile's RA products are what the math warps wait for next.
       uint32_t s_[2][16], g_[2][16];
@@ -498,12 +468,10 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       }
 
       // ---------------- half-step 2: RB ------------------------------------------
-      if (threadIdx.x == 0) ROW_TRACE(it, 7);
       ok = mbar_wait(bar_rb_full, it & 1, abort_flag, t.status, wait_code(KIND, 8));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if (threadIdx.x == 0) ROW_TRACE(it, 8);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const int c0 = half * 32 + ch * 16;
@@ -540,7 +508,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_op_full);
-      if (threadIdx.x == 0) ROW_TRACE(it, 9);
     }
 
     // ---------------- results ------------------------------------------------------
@@ -581,7 +548,6 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     if (n_iter > 0 && ok) ok = mbar_wait(bar_acc_done, 0, abort_flag, t.status, wait_code(KIND, 9));
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after_sync();
-    if (threadIdx.x == 0) ROW_TRACE(0, 12);
     // all accumulator columns of this thread first, then the arithmetic and the stores
     uint32_t v[kChunks][16];
 #pragma unroll
@@ -625,21 +591,8 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     store_tile_tma(&maps.out[MODE == ROW_PREDO ? TO_gdO : TO_gQ], strm_base, g.D, r0, bh, threadIdx.x == 0);
   }
 
-  if (threadIdx.x == 0) ROW_TRACE(0, 15);
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) ROW_TRACE(0, 13);
-#ifdef ATTN_EXPERIMENT
-  if (tracing && threadIdx.x < 256) t.trace[threadIdx.x] = strace[threadIdx.x];
-  if (threadIdx.x == 0 && t.trace != nullptr && g.debug <= -1 && blockIdx.x < 4096) {   // per-CTA record
-    unsigned smid;
-    asm("mov.u32 %0, %%smid;" : "=r"(smid));
-    t.trace[1024 + blockIdx.x * 4 + 0] = n_iter;
-    t.trace[1024 + blockIdx.x * 4 + 1] = clock64() - t_entry;
-    t.trace[1024 + blockIdx.x * 4 + 2] = smid;
-    t.trace[1024 + blockIdx.x * 4 + 3] = t_entry;
-  }
-#endif
   if (warp == kRowMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);

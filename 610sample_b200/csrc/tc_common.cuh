@@ -1,5 +1,5 @@
 // Definitions shared by the tensor-core kernel files: tile sizes, warp roles,
-// tensor-map bundle, shared-memory control block and small device helpers.
+// tensor-map bundle and small device helpers.
 #pragma once
 
 #include "attn_common.cuh"
@@ -12,13 +12,10 @@ constexpr int BM = 128;            // stationary rows per CTA
 constexpr int BN = 64;             // streamed rows per iteration
 constexpr int kMathWarps = 8;
 constexpr int kMathThreads = kMathWarps * 32;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8;   // the MMA-issuing warps follow it
 constexpr int kTmemCols = 512;
 constexpr uint32_t kAtomBytesStat = BM * 128;   // [128 rows][64 halves], 16 KB
 constexpr uint32_t kAtomBytesStrm = BN * 128;   // [ 64 rows][64 halves],  8 KB
-constexpr uint32_t kOpTileBytes = BM * 128;     // [128 rows][64 halves], 16 KB
 
 enum Kind { FWD_LSE = 0, FWD_OUT, BWD_ROW, BWD_COL, HVP_PRE, HVP_ROW, HVP_COL };
 enum TensorId { T_Q = 0, T_K, T_V, T_dO, T_gQ, T_gK, T_gV, T_COUNT };
@@ -29,17 +26,10 @@ enum OutId { TO_O = 0, TO_dQ = 0, TO_dK = 1, TO_dV = 2, TO_gdO = 0, TO_gQ = 1, T
 
 struct TmaMaps { CUtensorMap m[T_COUNT]; CUtensorMap out[TO_COUNT]; };
 
-// Shared-memory control block (lives in the aux area).
+// Control block of the single-tile self-test kernel (every attention kernel has its own).
 struct Control {
   uint64_t stat_full;
-  uint64_t stream_full[2];
-  uint64_t stream_empty[2];
-  uint64_t score_full[2];
-  uint64_t score_free[2];
-  uint64_t opnd_full;
-  uint64_t opnd_free;
   uint64_t acc_done;
-  uint64_t stats_ready[2];
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
