@@ -47,7 +47,7 @@ COL_KERNEL_GEMMS = 8
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture at 16 (batch, head)
 # slices (profiles/hvp_kernels_bf16_causal_N4096_D128_16heads_ncu_full.md); traffic grows in
 # proportion to the number of slices, so the bench scales it by BH / 16.
-NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 196.3e6, "row": 173.4e6, "col": 134.6e6}
+NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 193.1e6, "row": 170.4e6, "col": 137.4e6}
 
 
 def visible_pairs_causal(n: int) -> int:
@@ -337,16 +337,28 @@ def run_ours(args):
             "device_status": status,
         }
         if phase_ms and world == 1:
+            # One pass of the path = three launches (scalars + g_dO, g_Q, g_K + g_V).  `achieved` counts
+            # the 12 ALGORITHMIC contractions of the pass over the summed device time of the three
+            # kernels, each timed alone; `executed` adds what the tensor pipe really ran per kernel
+            # (score products are recomputed by each kernel), to be compared with ncu's
+            # sm__pipe_tensor_cycles_active.
             pairs = visible_pairs_causal(N) * BH
-            k_flops = {"pre": PRE_KERNEL_GEMMS, "row": ROW_KERNEL_GEMMS, "col": COL_KERNEL_GEMMS}
+            k_gemms = {"pre": PRE_KERNEL_GEMMS, "row": ROW_KERNEL_GEMMS, "col": COL_KERNEL_GEMMS}
+            total_ms = sum(phase_ms.values())
+            ach = 2.0 * D * HVP_GEMMS * pairs / (total_ms * 1e-3) / 1e12
             dom = max(phase_ms, key=phase_ms.get)
-            ach = 2.0 * D * k_flops[dom] * pairs / (phase_ms[dom] * 1e-3) / 1e12
-            line["roofline"] = {"bound": "tensor", "kernel": "hvp_" + dom, "achieved": ach, "peak": peaks["bf16_tflops"],
+            executed = {k: {"gemms": k_gemms[k], "tflops": 2.0 * D * k_gemms[k] * pairs / (phase_ms[k] * 1e-3) / 1e12}
+                        for k in phase_ms}
+            for k in executed:
+                executed[k]["frac"] = executed[k]["tflops"] / peaks["bf16_tflops"]
+            line["roofline"] = {"bound": "tensor", "kernel": "hvp pass = hvp_row<PREDO> + hvp_row<Q> + hvp_col",
+                                "achieved": ach, "peak": peaks["bf16_tflops"],
                                 "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
-                                "traffic": NCU_TRAFFIC_BYTES_16_SLICES[dom] * BH / 16.0,
-                                "traffic_note": "bytes per launch, scaled from an ncu capture at 16 slices",
-                                "peak_source": peaks["source"],
-                                "kernel_ms": phase_ms, "gemms_counted": k_flops[dom]}
+                                "traffic": sum(NCU_TRAFFIC_BYTES_16_SLICES.values()) * BH / 16.0,
+                                "traffic_note": "dram bytes of the three launches, scaled from an ncu capture at 16 slices; "
+                                                "algorithmic bytes of the pass: %.0f" % ((12 * N * D * 2 + 4 * N) * BH),
+                                "peak_source": peaks["source"], "kernel_ms": phase_ms,
+                                "dominant_kernel": "hvp_" + dom, "executed": executed}
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
             n_cpu = 16
