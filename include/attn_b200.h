@@ -52,8 +52,9 @@ enum {
 };
 
 /* Which kernel family serves a call.  AUTO picks the tcgen05 tensor-core
- * kernels for f16/bf16 with D in {64, 128} and the fp32 SIMT kernels otherwise
- * (f32 inputs, D in {16, 32, 48, 80, 96, 112}). */
+ * kernels for f16/bf16 inputs (every supported D; head dimensions other than
+ * 64 and 128 run zero-padded to the next of the two) and the fp32 SIMT kernels
+ * for f32 inputs. */
 enum { ATTN_IMPL_AUTO = 0, ATTN_IMPL_SIMT = 1, ATTN_IMPL_TENSOR = 2 };
 
 typedef struct attn_shape {
