@@ -162,6 +162,20 @@ def test_tensor_kernels_agree_with_simt_at_n2048():
             assert float((a[n] - b[n]).abs().max()) <= tol, n
 
 
+def test_grouped_cta_order_with_a_partial_last_group():
+    """300 (batch, head) slices of 4 row tiles: more than 8 waves of CTAs, so the kernels take the
+    heads in groups of 64 with a last group of 44.  Tensor-core kernels against the SIMT kernels."""
+    inp = orc.make_inputs(3, 100, 512, 512, 64, seed=8, dtype=torch.bfloat16)
+    a = run_all(inp, 512, 0, 0, 2)
+    b = run_all(inp, 512, 0, 0, 1)
+    for n in orc.OUTPUT_NAMES:
+        if n == "L":
+            assert (a[n] - b[n]).abs().max() < 1e-4
+        else:
+            tol = HALF_RTOL[torch.bfloat16] * max(1.0, float(b[n].abs().max()))
+            assert float((a[n] - b[n]).abs().max()) <= tol, n
+
+
 def test_linearity_in_tangents_at_headline_size():
     """Size-independent property at N=4096, D=128 causal: the HVP is linear in the tangents,
     HVP(a*g) == a*HVP(g) exactly for a power of two, and HVP(0) == 0."""
