@@ -367,6 +367,23 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
     float acc_m = -INFINITY, acc_l = 0.f;        // FWD_LSE: running maximum and sum (log2 domain)
     float2 p_[16];                               // backward kinds: carried from S to dP
 
+    // BWD_COL: per-query scalars of a streamed tile, fetched one tile ahead by the first four warps
+    // (thread -> (which, query)) and handed over in shared memory; every warp arrives on the barrier.
+    auto fetch_stat = [&](int tile_it) {
+      const int which = (threadIdx.x >> 6) & 1, c = threadIdx.x & 63;
+      const int qi = (t_begin + tile_it) * BN + c;
+      float v = (which == 0) ? -INFINITY : 0.f;
+      if (CF::kCol && threadIdx.x < 128 && tile_it < n_iter && qi < g.N_q)
+        v = (which == 0) ? -__ldg(t.L + row_off + qi) * kLog2e : -__ldg(t.Dv + row_off + qi);
+      return v;
+    };
+    auto publish_stat = [&](int tile_it, float v) {
+      if (threadIdx.x < 128) aux_f[(tile_it & 1) * 128 + (threadIdx.x >> 6) * 64 + (threadIdx.x & 63)] = v;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->stats_ready[tile_it & 1]));
+    };
+    if constexpr (CF::kCol) { if (n_iter > 0) publish_stat(0, fetch_stat(0)); }
+
     for (int it = 0; it < n_iter && ok; ++it) {
       const int b = it % kBufs;
       const int j0 = (t_begin + it) * BN;
@@ -375,18 +392,11 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
       const uint32_t ra = lane_addr + CF::kRA + 64 * b + half * 32;
       const uint32_t rb = lane_addr + CF::kRB + 64 * b + half * 32;
       const float* cs = aux_f + (it & 1) * 128;   // BWD_COL: [-L*log2(e) | -Dv] x 64 queries
+      float next_stat = 0.f;
       if constexpr (CF::kCol) {
-        if (threadIdx.x < 128) {
-          const int which = threadIdx.x >> 6, c = threadIdx.x & 63;
-          const int qi = j0 + c;
-          float v = (which == 0) ? -INFINITY : 0.f;
-          if (qi < g.N_q) v = (which == 0) ? -t.L[row_off + qi] * kLog2e : -t.Dv[row_off + qi];
-          aux_f[(it & 1) * 128 + which * 64 + c] = v;
-        }
-        __syncwarp();
-        const uint32_t bar = smem_u32(&ctl->stats_ready[it & 1]);
-        if (lane == 0) mbar_arrive(bar);
-        ok = mbar_wait(bar, (it >> 1) & 1, abort_flag, t.status, wait_code(KCODE, 9));
+        // the scalars of tile it+1 are fetched now and published at the end of this tile
+        next_stat = fetch_stat(it + 1);
+        ok = mbar_wait(smem_u32(&ctl->stats_ready[it & 1]), (it >> 1) & 1, abort_flag, t.status, wait_code(KCODE, 9));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -484,6 +494,9 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_op_full(b));
+      // every warp has finished the previous tile (its operands were consumed before this tile's
+      // dP^T product was queued), so the other scalar buffer is free
+      if constexpr (CF::kCol) { if (it + 1 < n_iter) publish_stat(it + 1, next_stat); }
     }
 
     // ---------------- results ------------------------------------------------------
