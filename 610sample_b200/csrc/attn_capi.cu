@@ -314,7 +314,8 @@ int attn_b200_double_backward_static(const attn_shape_t* shape, const void* g_dQ
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (use_tc) {
     const char* why = nullptr;
-    e = attn::launch_tc(attn::OP_DOUBLE_BACKWARD, shape->dtype, g, t, cs, &tl_launches, &why, attn::HVP_PHASE_ALL);
+    e = attn::launch_tc(attn::OP_DOUBLE_BACKWARD, shape->dtype, g, t, cs, &tl_launches, &why,
+                        attn::HVP_PHASE_ALL | attn::HVP_PHASE_SERIAL);   // no helper stream: this entry creates nothing
     if (e != cudaSuccess)
       return fail(ATTN_ECUDA, "tensor-core launch failed: %s%s%s", cudaGetErrorString(e), why ? ": " : "", why ? why : "");
   } else {

@@ -9,7 +9,9 @@ enum Op { OP_FORWARD = 0, OP_BACKWARD = 1, OP_DOUBLE_BACKWARD = 2 };
 
 // Phases of the double backward, as a bit mask (all = 7).  PRE computes the
 // per-row scalars into scratch, ROW the query-side outputs, COL the key-side ones.
-enum HvpPhase { HVP_PHASE_PRE = 1, HVP_PHASE_ROW = 2, HVP_PHASE_COL = 4, HVP_PHASE_ALL = 7 };
+enum HvpPhase { HVP_PHASE_PRE = 1, HVP_PHASE_ROW = 2, HVP_PHASE_COL = 4, HVP_PHASE_ALL = 7,
+                // internal: keep every launch on the caller's stream (no helper stream is created)
+                HVP_PHASE_SERIAL = 8 };
 
 // fp32 CUDA-core kernels: any dtype, D a multiple of 16 up to 128.
 cudaError_t launch_simt(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,

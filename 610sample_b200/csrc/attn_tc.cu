@@ -233,6 +233,51 @@ cudaError_t launch_hvp_row(int mode, int D, int is_bf16, const TmaMaps& maps, co
 cudaError_t launch_fwd_bwd(int kind, int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
                            cudaStream_t s);
 
+// Kernels of one operation that do not depend on one another (g_Q and g_K/g_V of the double
+// backward; dQ and dK/dV of the backward) run side by side: the second is launched on a helper
+// stream of the device between an event fork and an event join on the caller's stream, so the
+// SMs that one kernel's last CTAs leave idle take CTAs of the other.  The pattern is legal under
+// stream capture.  One helper stream and two events per device, created on first use; when that
+// fails the launches stay on the caller's stream.
+struct Helper { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool tried = false; };
+
+static Helper* helper_for_current_device() {
+  static Helper helpers[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  Helper& h = helpers[dev];
+  if (!h.tried) {
+    h.tried = true;
+    if (cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&h.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&h.join, cudaEventDisableTiming) != cudaSuccess) {
+      (void)cudaGetLastError();
+      h.stream = nullptr;
+    }
+  }
+  return h.stream != nullptr ? &h : nullptr;
+}
+
+// first(s) and second(helper stream) between fork and join; serial on s without a helper
+template <typename F1, typename F2>
+static cudaError_t run_side_by_side(cudaStream_t s, bool allow_helper, F1 first, F2 second) {
+  Helper* h = allow_helper ? helper_for_current_device() : nullptr;
+  if (h == nullptr || cudaEventRecord(h->fork, s) != cudaSuccess ||
+      cudaStreamWaitEvent(h->stream, h->fork, 0) != cudaSuccess) {
+    (void)cudaGetLastError();
+    cudaError_t e = first(s);
+    return e == cudaSuccess ? second(s) : e;
+  }
+  cudaError_t e1 = first(s);
+  cudaError_t e2 = second(h->stream);
+  // the join is made even after a failed launch, so that the helper stream never outlives the call
+  cudaError_t ej = cudaEventRecord(h->join, h->stream);
+  if (ej == cudaSuccess) ej = cudaStreamWaitEvent(s, h->join, 0);
+  return e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : ej;
+}
+
 template <typename T>
 static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, const Tensors& t, cudaStream_t s,
                              int* n, int phases) {
@@ -251,13 +296,23 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
       rowdot_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)t.dO, (const T*)t.O, t.Dv, rows, g.D);
       e = cudaGetLastError();
     }
-    if (e == cudaSuccess) e = launch_fwd_bwd(2, D, bf, maps, g, t, s);    // dQ
-    if (e == cudaSuccess) e = launch_fwd_bwd(3, D, bf, maps, g, t, s);    // dK, dV
+    if (e == cudaSuccess)
+      e = run_side_by_side(s, true,
+                           [&](cudaStream_t q) { return launch_fwd_bwd(2, D, bf, maps, g, t, q); },     // dQ
+                           [&](cudaStream_t q) { return launch_fwd_bwd(3, D, bf, maps, g, t, q); });    // dK, dV
     *n = 3;
   } else {
     if (phases & HVP_PHASE_PRE) { e = launch_hvp_row(0, D, bf, maps, g, t, s); ++*n; }                        // scalars + g_dO
-    if (e == cudaSuccess && (phases & HVP_PHASE_ROW)) { e = launch_hvp_row(1, D, bf, maps, g, t, s); ++*n; }  // g_Q
-    if (e == cudaSuccess && (phases & HVP_PHASE_COL)) { e = launch_hvp_col(D, bf, maps, g, t, s); ++*n; }     // g_K, g_V
+    const bool row = (phases & HVP_PHASE_ROW) != 0, col = (phases & HVP_PHASE_COL) != 0;
+    if (e == cudaSuccess && row && col) {
+      e = run_side_by_side(s, (phases & HVP_PHASE_SERIAL) == 0,
+                           [&](cudaStream_t q) { return launch_hvp_col(D, bf, maps, g, t, q); },        // g_K, g_V
+                           [&](cudaStream_t q) { return launch_hvp_row(1, D, bf, maps, g, t, q); });    // g_Q
+      *n += 2;
+    } else {
+      if (e == cudaSuccess && row) { e = launch_hvp_row(1, D, bf, maps, g, t, s); ++*n; }  // g_Q
+      if (e == cudaSuccess && col) { e = launch_hvp_col(D, bf, maps, g, t, s); ++*n; }     // g_K, g_V
+    }
   }
   return e;
 }
