@@ -239,7 +239,12 @@ cudaError_t launch_fwd_bwd(int kind, int D, int is_bf16, const TmaMaps& maps, co
 // SMs that one kernel's last CTAs leave idle take CTAs of the other.  The pattern is legal under
 // stream capture.  One helper stream and two events per device, created on first use; when that
 // fails the launches stay on the caller's stream.
-struct Helper { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool tried = false; };
+struct Helper {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool tried = false;
+  std::mutex in_use;   // host threads share the events: one fork ... join sequence at a time
+};
 
 static Helper* helper_for_current_device() {
   static Helper helpers[64];
@@ -264,8 +269,12 @@ static Helper* helper_for_current_device() {
 template <typename F1, typename F2>
 static cudaError_t run_side_by_side(cudaStream_t s, bool allow_helper, F1 first, F2 second) {
   Helper* h = allow_helper ? helper_for_current_device() : nullptr;
-  if (h == nullptr || cudaEventRecord(h->fork, s) != cudaSuccess ||
-      cudaStreamWaitEvent(h->stream, h->fork, 0) != cudaSuccess) {
+  if (h == nullptr) {
+    cudaError_t e = first(s);
+    return e == cudaSuccess ? second(s) : e;
+  }
+  std::lock_guard<std::mutex> lock(h->in_use);
+  if (cudaEventRecord(h->fork, s) != cudaSuccess || cudaStreamWaitEvent(h->stream, h->fork, 0) != cudaSuccess) {
     (void)cudaGetLastError();
     cudaError_t e = first(s);
     return e == cudaSuccess ? second(s) : e;
