@@ -268,7 +268,7 @@ def run_ours(args):
     # The (batch, head) slices are independent, so the host-buffer path is pipelined over
     # chunks of slices on three streams: upload of chunk c+1, kernels of chunk c and download
     # of chunk c-1 overlap (PCIe is full duplex).  Every byte still crosses inside the timed region.
-    n_chunks = 4 if bh_local % 4 == 0 else 1
+    n_chunks = args.e2e_chunks if (args.e2e_chunks > 0 and bh_local % args.e2e_chunks == 0) else 1
     per = bh_local // n_chunks
     s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
 
@@ -379,6 +379,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks of slices the host-buffer leg is pipelined over")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--bh", type=int, default=0,
                     help="profiling only: number of (batch, head) slices instead of the workload's 64")
