@@ -1,7 +1,7 @@
 // Forward and first-backward attention kernels on sm_100a (f16/bf16, D a multiple of 16 up to 128).
 //
 // Four kinds of one kernel.  A CTA owns 128 STATIONARY rows of one (batch, head) and streams
-// 64-row tiles of the other axis through four TMA stages:
+// 64-row tiles of the other axis through as many TMA stages as fit in shared memory (five to eight):
 //
 //   kind      stationary     streamed   tensor-memory score regions        produces
 //   FWD_LSE   Q              K          RA = S                 (x2)        L = log-sum-exp
@@ -32,13 +32,13 @@ enum FbKind { FB_FWD_LSE = 0, FB_FWD_OUT, FB_BWD_ROW, FB_BWD_COL };
 
 constexpr int kFbMmaWarp = 9;
 constexpr int kFbThreads = 320;
-constexpr int kFbStages = 4;
+constexpr int kFbMaxStages = 8;
 
 struct FbControl {
   uint64_t staging_full;
   uint64_t stat_ready;
-  uint64_t stream_full[kFbStages];
-  uint64_t stream_empty[kFbStages];
+  uint64_t stream_full[kFbMaxStages];
+  uint64_t stream_empty[kFbMaxStages];
   uint64_t ra_full[2];
   uint64_t rb_full[2];
   uint64_t op_full[2];       // math warps are done with the regions of a tile (operands written)
@@ -61,7 +61,13 @@ struct FbCfg {
   static constexpr uint32_t kStagingBytes = kNStat * kAtoms * kAtomBytesStat;
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
   static constexpr uint32_t kAuxBytes = 512 + 2048;   // control; per-query scalars / L exchange
-  static constexpr uint32_t kContentBytes = kStagingBytes + kFbStages * kStageBytes + kAuxBytes;
+  // as many stream stages as fit (at most eight): a TMA load takes about 2 000 clocks from request
+  // to arrival and a tile of these kernels much less, so the loads have to run several tiles ahead
+  static constexpr uint32_t kMaxSmem = 232448;
+  static constexpr int kFit = (int)((kMaxSmem - 1024 - kStagingBytes - kAuxBytes) / kStageBytes);
+  static constexpr int kStages = kFit < kFbMaxStages ? kFit : kFbMaxStages;
+  static_assert(kStages >= 3, "too few stream stages");
+  static constexpr uint32_t kContentBytes = kStagingBytes + kStages * kStageBytes + kAuxBytes;
   static constexpr uint32_t kSmemBytes = kContentBytes + 1024;
   // tensor-memory columns
   static constexpr int kRA = 0;
@@ -98,7 +104,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
   }
   const uint32_t staging = smem_base;
   const uint32_t strm_base = staging + CF::kStagingBytes;
-  const uint32_t aux_off = CF::kStagingBytes + kFbStages * CF::kStageBytes;
+  const uint32_t aux_off = CF::kStagingBytes + CF::kStages * CF::kStageBytes;
   FbControl* ctl = reinterpret_cast<FbControl*>(smem_gen + aux_off);
   float* aux_f = reinterpret_cast<float*>(smem_gen + aux_off + 512);   // 512 floats
 
@@ -127,7 +133,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
   if (threadIdx.x == 0) {
     mbar_init(bar_staging_full, 1);
     mbar_init(bar_stat_ready, kMathWarps);
-    for (int s = 0; s < kFbStages; ++s) {
+    for (int s = 0; s < CF::kStages; ++s) {
       mbar_init(bar_stream_full(s), 1);
       mbar_init(bar_stream_empty(s), 1);
     }
@@ -169,8 +175,8 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
                         &maps.m[CF::stat_tensor(x)], a * 64, r0 + h * 64, bh, bar_staging_full);
       bool ok = true;
       for (int it = 0; it < n_iter; ++it) {
-        const int st = it % kFbStages;
-        ok = mbar_wait(bar_stream_empty(st), ((it / kFbStages) & 1) ^ 1, abort_flag, t.status, wait_code(KCODE, 1));
+        const int st = it % CF::kStages;
+        ok = mbar_wait(bar_stream_empty(st), ((it / CF::kStages) & 1) ^ 1, abort_flag, t.status, wait_code(KCODE, 1));
         if (!ok) break;
         mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
         const uint32_t stage = strm_base + st * CF::kStageBytes;
@@ -211,9 +217,9 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
       const uint32_t out0 = tmem_base + CF::kOut, out1 = out0 + D;
       (void)stat1; (void)out1;
 
-      auto stage_of = [&](int j) { return strm_base + (uint32_t)(j % kFbStages) * CF::kStageBytes; };
+      auto stage_of = [&](int j) { return strm_base + (uint32_t)(j % CF::kStages) * CF::kStageBytes; };
       auto wait_stream = [&](int j) {
-        bool w = mbar_wait(bar_stream_full(j % kFbStages), (j / kFbStages) & 1, abort_flag, t.status, wait_code(KCODE, 3));
+        bool w = mbar_wait(bar_stream_full(j % CF::kStages), (j / CF::kStages) & 1, abort_flag, t.status, wait_code(KCODE, 3));
         return (bool)__all_sync(0xffffffffu, w);
       };
       // Every batch of products is issued by the elected lane inside one branch, with the
@@ -287,7 +293,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         if (!ok) break;
         tc_fence_after_sync();
         if constexpr (CF::kNOut > 0) issue_out(j);
-        commit(bar_stream_empty(j % kFbStages));    // every product reading this stage has been issued
+        commit(bar_stream_empty(j % CF::kStages));    // every product reading this stage has been issued
         const int nj = j + kBufs;
         if (nj < n_iter) {
           if constexpr (CF::kCol) {

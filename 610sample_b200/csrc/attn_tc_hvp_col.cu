@@ -2,7 +2,7 @@
 // given the per-row scalars Dv, dot2, dot3 of the row-side pre-pass.
 //
 // A CTA owns 128 key rows (stationary K, V, g_dK, g_dV in shared memory) and streams 64-row
-// query tiles (Q, g_dQ, dO; two TMA stages).  Scores are computed TRANSPOSED (keys on the
+// query tiles (Q, g_dQ, dO; two TMA stages at D = 128, six at D = 64).  Scores are computed TRANSPOSED (keys on the
 // tensor-memory lanes), so the operand roles are those of the row kernels.
 // Tensor memory (512 columns):
 //     RA [  0,128) = [ S^T | gdS^T ] = K [Q; g_dQ]^T (one N = 128 product), gdS^T += g_dK Q^T
@@ -31,14 +31,15 @@ namespace attn {
 namespace tc {
 
 constexpr int kColMmaWarp = 9;
+constexpr int kColMaxStages = 6;
 
 constexpr int kColThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
 
-struct ColControl {
+struct ColControl {   // lives in the first 256 bytes of the aux area
   uint64_t stat_full;
-  uint64_t stream_full[2];     // Q and g_dQ of a streamed tile have landed
-  uint64_t stream_full_do[2];  // its dO has landed
-  uint64_t stream_empty[2];
+  uint64_t stream_full[kColMaxStages];     // Q and g_dQ of a streamed tile have landed
+  uint64_t stream_full_do[kColMaxStages];  // its dO has landed
+  uint64_t stream_empty[kColMaxStages];
   uint64_t ra_full, ra_free;
   uint64_t rb_full;
   uint64_t op_half;            // operands of the even k-steps (first 16 queries of each half) written
@@ -49,6 +50,8 @@ struct ColControl {
   volatile uint32_t abort_flag;
 };
 
+static_assert(sizeof(ColControl) <= 256, "control block larger than its slot");
+
 template <int D>
 struct ColCfg {
   static constexpr int kAtoms = D / 64;
@@ -57,7 +60,11 @@ struct ColCfg {
   static constexpr uint32_t kStatBytes = kNStat * kAtoms * kAtomBytesStat;
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
   static constexpr uint32_t kAuxBytes = 256 + 2048;   // control block + [2][4][64] per-query scalars
-  static constexpr uint32_t kContentBytes = kStatBytes + 2 * kStageBytes + kAuxBytes;
+  // 128 KB of stationary operands leave room for two 48 KB stages at D = 128; at D = 64 both halve
+  // and six stages fit, which covers the latency of a TMA load (about 2 000 clocks)
+  static constexpr int kStages = (D == 64) ? 6 : 2;
+  static_assert(kStages <= kColMaxStages, "control block too small");
+  static constexpr uint32_t kContentBytes = kStatBytes + kStages * kStageBytes + kAuxBytes;
   static constexpr uint32_t kMaxSmem = 232448;
   static_assert(kContentBytes + 768 <= kMaxSmem, "shared memory over-subscribed");
   static constexpr uint32_t kSmemBytes = (kContentBytes + 1024 <= kMaxSmem) ? kContentBytes + 1024 : kMaxSmem;
@@ -98,7 +105,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   }
   const uint32_t stat_base = smem_base;
   const uint32_t strm_base = stat_base + CF::kStatBytes;
-  const uint32_t aux_off = CF::kStatBytes + 2 * CF::kStageBytes;
+  const uint32_t aux_off = CF::kStatBytes + CF::kStages * CF::kStageBytes;
   ColControl* ctl = reinterpret_cast<ColControl*>(smem_gen + aux_off);
   float* col_stats = reinterpret_cast<float*>(smem_gen + aux_off + 256);   // [2][4][64]
 
@@ -124,12 +131,12 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
   if (threadIdx.x == 0) {
     mbar_init(bar_stat_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < CF::kStages; ++s) {
       mbar_init(bar_stream_full(s), 1);
       mbar_init(bar_stream_full_do(s), 1);
       mbar_init(bar_stream_empty(s), 1);
-      mbar_init(smem_u32(&ctl->stats_ready[s]), kMathWarps);
     }
+    for (int s = 0; s < 2; ++s) mbar_init(smem_u32(&ctl->stats_ready[s]), kMathWarps);
     mbar_init(bar_ra_full, 1);
     mbar_init(bar_ra_free, kMathWarps);
     mbar_init(bar_rb_full, 1);
@@ -180,8 +187,8 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     if (lane == 0 && n_iter > 0) {
       bool ok = true;
       for (int it = 1; it < n_iter; ++it) {     // tile 0 was requested above
-        const int st = it & 1;
-        ok = mbar_wait(bar_stream_empty(st), ((it >> 1) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
+        const int st = it % CF::kStages;
+        ok = mbar_wait(bar_stream_empty(st), ((it / CF::kStages) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
         if (!ok) break;
         // Q and g_dQ first, on their own barrier: the RA products of the tile need only them
         mbar_arrive_expect_tx(bar_stream_full(st), 2 * kAtoms * kAtomBytesStrm);
@@ -293,10 +300,10 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       // waits for RA(j) to have been read, and RB(j+1) follows OUT(j), which reads RB, in the
       // second warp's own order.
       auto wait_stream = [&](int tile) {       // Q and g_dQ of the tile
-        return mbar_wait(bar_stream_full(tile & 1), (tile >> 1) & 1, abort_flag, t.status, wait_code(KIND, 3));
+        return mbar_wait(bar_stream_full(tile % CF::kStages), (tile / CF::kStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
       };
       auto wait_stream_do = [&](int tile) {    // dO of the tile
-        return mbar_wait(bar_stream_full_do(tile & 1), (tile >> 1) & 1, abort_flag, t.status, wait_code(KIND, 13));
+        return mbar_wait(bar_stream_full_do(tile % CF::kStages), (tile / CF::kStages) & 1, abort_flag, t.status, wait_code(KIND, 13));
       };
       if (warp == kColMmaWarp) {
         // ---- first warp: the RA products of every tile
@@ -306,7 +313,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t stage = strm_base + (j & 1) * CF::kStageBytes;
+          const uint32_t stage = strm_base + (j % CF::kStages) * CF::kStageBytes;
           issue_ra_head(stage);
           issue_ra_tail(stage);
         }
@@ -319,7 +326,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           issue_rb_head(strm_base); issue_rb_tail(strm_base);
         }
         for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j & 1, nst = st ^ 1;
+          const int st = j % CF::kStages, nst = (j + 1) % CF::kStages;
           const bool more = j + 1 < n_iter;
           ok = mbar_wait(bar_op_half, j & 1, abort_flag, t.status, wait_code(KIND, 14));
           ok = __all_sync(0xffffffffu, ok);

@@ -10,7 +10,7 @@
 //              applied in the epilogue instead of inside the loop)
 //   ROW_Q      g_Q = s (dS g_dK + g_S K), given the scalars
 //
-// Both stream K, g_dK, V, g_dV in 64-row tiles (three TMA stages) past 128 stationary
+// Both stream K, g_dK, V, g_dV in 64-row tiles (three TMA stages, six at D = 64) past 128 stationary
 // rows of Q, dO, g_dQ.  Q and dO are copied once into TENSOR MEMORY and used from there
 // as the A operand of their score products (an A operand in shared memory is re-read by
 // every MMA instruction: measured 48 instead of 32 clocks for an N = 64 product); g_dQ
@@ -42,14 +42,14 @@ enum RowMode { ROW_PREDO = 0, ROW_Q = 1 };
 constexpr int kRowMmaWarp = 9;
 constexpr int kRowThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
 
-constexpr int kRowStages = 3;
+constexpr int kRowMaxStages = 6;
 
 struct RowControl {
   uint64_t stat_full;          // g_dQ tile in shared memory
-  uint64_t staging_full;       // Q and dO tiles in the staging buffer (stage 2)
+  uint64_t staging_full;       // Q and dO tiles in the staging buffer (the last stage)
   uint64_t stat_tmem_ready;    // Q and dO copied to tensor memory
-  uint64_t stream_full[kRowStages];
-  uint64_t stream_empty[kRowStages];
+  uint64_t stream_full[kRowMaxStages];
+  uint64_t stream_empty[kRowMaxStages];
   uint64_t ra_full;
   uint64_t ra_free;
   uint64_t rb_full;
@@ -60,15 +60,22 @@ struct RowControl {
   volatile uint32_t abort_flag;
 };
 
+static_assert(sizeof(RowControl) <= 256, "control block larger than its slot");
+
 template <int D>
 struct RowCfg {
   static constexpr int kAtoms = D / 64;
   static constexpr int kNStream = 4;    // K, g_dK, V, g_dV (pairs back to back)
+  // A TMA load takes about 2 000 clocks from request to arrival, whatever its size.  At D = 128
+  // a tile takes longer than that and three stages (all that fits) keep the loads ahead; at
+  // D = 64 a tile takes about 1 600 clocks and the stages are half the size: six of them.
+  static constexpr int kStages = (D == 64) ? 6 : 3;
+  static_assert(kStages <= kRowMaxStages, "control block too small");
   static constexpr uint32_t kStatBytes = kAtoms * kAtomBytesStat;            // g_dQ only
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
   static_assert(kStageBytes == 2 * kAtoms * kAtomBytesStat, "Q and dO are staged in one stream stage");
   static constexpr uint32_t kAuxBytes = 256;          // control block
-  static constexpr uint32_t kContentBytes = kStatBytes + kRowStages * kStageBytes + kAuxBytes;
+  static constexpr uint32_t kContentBytes = kStatBytes + kStages * kStageBytes + kAuxBytes;
   static constexpr uint32_t kMaxSmem = 232448;
   static_assert(kContentBytes <= kMaxSmem, "shared memory over-subscribed");
   static constexpr uint32_t kSmemBytes = (kContentBytes + 1024 <= kMaxSmem) ? kContentBytes + 1024 : kMaxSmem;
@@ -105,8 +112,8 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   }
   const uint32_t stat_base = smem_base;
   const uint32_t strm_base = stat_base + CF::kStatBytes;
-  const uint32_t aux_off = CF::kStatBytes + kRowStages * CF::kStageBytes;
-  const uint32_t staging = strm_base + 2 * CF::kStageBytes;   // Q then dO, before the third stage is used
+  const uint32_t aux_off = CF::kStatBytes + CF::kStages * CF::kStageBytes;
+  const uint32_t staging = strm_base + (CF::kStages - 1) * CF::kStageBytes;   // Q then dO, before the last stage is used
   RowControl* ctl = reinterpret_cast<RowControl*>(smem_gen + aux_off);
   // [2 halves][4][128] floats of row sums, exchanged after the last product has read the
   // g_dQ tile: its shared memory is reused
@@ -138,7 +145,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     mbar_init(bar_stat_full, 1);
     mbar_init(bar_staging_full, 1);
     mbar_init(bar_stat_tmem_ready, kMathWarps);
-    for (int s = 0; s < kRowStages; ++s) {
+    for (int s = 0; s < CF::kStages; ++s) {
       mbar_init(bar_stream_full(s), 1);
       mbar_init(bar_stream_empty(s), 1);
     }
@@ -195,10 +202,10 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     if (lane == 0 && n_iter > 0) {
       bool ok = true;
       for (int it = 1; it < n_iter; ++it) {     // tile 0 was requested above
-        const int st = it % kRowStages;
-        ok = mbar_wait(bar_stream_empty(st), ((it / kRowStages) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
-        // the third stage doubles as the staging buffer of Q and dO until they are in tensor memory
-        if (ok && it == 2) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 10));
+        const int st = it % CF::kStages;
+        ok = mbar_wait(bar_stream_empty(st), ((it / CF::kStages) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
+        // the last stage doubles as the staging buffer of Q and dO until they are in tensor memory
+        if (ok && it == CF::kStages - 1) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 10));
         if (!ok) break;
         mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
         const uint32_t stage = strm_base + st * CF::kStageBytes;
@@ -303,7 +310,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       // waits for RA(j) to have been read, and RB(j+1) follows OUT(j), which reads RB, in the
       // second warp's own order.
       auto wait_stream = [&](int tile) {
-        return mbar_wait(bar_stream_full(tile % kRowStages), (tile / kRowStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
+        return mbar_wait(bar_stream_full(tile % CF::kStages), (tile / CF::kStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
       };
       if (warp == kRowMmaWarp) {
         // ---- first warp: the RA products of every tile
@@ -317,7 +324,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t stage = strm_base + (j % kRowStages) * CF::kStageBytes;
+          const uint32_t stage = strm_base + (j % CF::kStages) * CF::kStageBytes;
           issue_ra_head(stage, j);
           issue_ra_tail(stage);
         }
@@ -331,7 +338,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           if (lane == 0) mbar_arrive(bar_rb_issued);
         }
         for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j % kRowStages, nst = (j + 1) % kRowStages;
+          const int st = j % CF::kStages, nst = (j + 1) % CF::kStages;
           const bool more = j + 1 < n_iter;
           ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
           if (ok && more) ok = wait_stream(j + 1);
