@@ -52,8 +52,8 @@ struct RowControl {
   uint64_t stream_empty[kRowMaxStages];
   uint64_t ra_full;
   uint64_t ra_free;
-  uint64_t rb_full;
-  uint64_t op_full;
+  uint64_t rb_full[2];         // per RB buffer
+  uint64_t op_full[2];         // per RB buffer: operands of a tile written
   uint64_t acc_done;
   uint64_t rb_issued;          // second issuing warp -> first: the RB products of a tile are queued
   uint32_t tmem_base;
@@ -79,7 +79,12 @@ struct RowCfg {
   static constexpr uint32_t kMaxSmem = 232448;
   static_assert(kContentBytes <= kMaxSmem, "shared memory over-subscribed");
   static constexpr uint32_t kSmemBytes = (kContentBytes + 1024 <= kMaxSmem) ? kContentBytes + 1024 : kMaxSmem;
-  static constexpr int kRA = 0, kRB = 128, kOut = 256, kQT = 384, kDOT = 448;
+  // At D = 64 the accumulator and the stationary operands take half the columns, which leaves
+  // room for a second RB region: the RB products then run a tile ahead of the outputs instead of
+  // waiting behind them, and the math warps (the bound at D = 64) never wait for RB.
+  static constexpr int kRbBufs = (D == 64) ? 2 : 1;
+  static constexpr int kRA = 0, kRB = 128, kOut = 128 + 128 * kRbBufs;
+  static constexpr int kQT = (D == 64) ? 448 : 384, kDOT = (D == 64) ? 480 : 448;
   static_assert(kOut + D <= kQT && kQT + D / 2 <= kDOT && kDOT + D / 2 <= kTmemCols, "tensor memory over-subscribed");
   __host__ __device__ static constexpr uint32_t stream_off(int slot, int atom) {
     return (uint32_t)(slot >> 1) * (2u * kAtoms * kAtomBytesStrm) + (uint32_t)atom * 2u * kAtomBytesStrm +
@@ -135,8 +140,10 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t bar_staging_full = smem_u32(&ctl->staging_full);
   const uint32_t bar_stat_tmem_ready = smem_u32(&ctl->stat_tmem_ready);
   const uint32_t bar_ra_full = smem_u32(&ctl->ra_full), bar_ra_free = smem_u32(&ctl->ra_free);
-  const uint32_t bar_rb_full = smem_u32(&ctl->rb_full);
-  const uint32_t bar_op_full = smem_u32(&ctl->op_full), bar_acc_done = smem_u32(&ctl->acc_done);
+  auto bar_rb_full = [&](int b) { return smem_u32(&ctl->rb_full[b]); };
+  auto bar_op_full = [&](int b) { return smem_u32(&ctl->op_full[b]); };
+  const uint32_t bar_acc_done = smem_u32(&ctl->acc_done);
+  constexpr int LA = CF::kRbBufs;     // tiles the RB products run ahead of the outputs
   const uint32_t bar_rb_issued = smem_u32(&ctl->rb_issued);
   auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
   auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
@@ -151,8 +158,10 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     }
     mbar_init(bar_ra_full, 1);
     mbar_init(bar_ra_free, kMathWarps);
-    mbar_init(bar_rb_full, 1);
-    mbar_init(bar_op_full, kMathWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_rb_full(b), 1);
+      mbar_init(bar_op_full(b), kMathWarps);
+    }
     mbar_init(bar_acc_done, 1);
     mbar_init(bar_rb_issued, 1);
     ctl->abort_flag = 0u;
@@ -275,32 +284,25 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         }
         __syncwarp();
       };
-      auto issue_rb_head = [&](uint32_t stage) {
+      auto issue_rb = [&](uint32_t stage, int b) {    // into RB buffer b; ends with its commit
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        const uint32_t acc = rb + 128u * (uint32_t)b;
         if (elect_one()) {
-          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)
-            if (ks < ks_n) mma_ts(rb, dot + 8 * ks, dk + koff(2, ks), kIdesc128, ks > 0);
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+            if (ks < ks_n) mma_ts(acc, dot + 8 * ks, dk + koff(2, ks), kIdesc128, ks > 0);
+          mma_commit(bar_rb_full(b));
         }
         __syncwarp();
       };
-      auto issue_rb_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
-        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
-        if (elect_one()) {
-          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
-            if (ks < ks_n) mma_ts(rb, dot + 8 * ks, dk + koff(2, ks), kIdesc128, ks > 0);
-          mma_commit(bar_rb_full);
-        }
-        __syncwarp();
-      };
-      auto issue_out = [&](uint32_t stage, bool first) {
+      auto issue_out = [&](uint32_t stage, bool first, int b) {   // operands in RB buffer b
         const uint64_t dm = smem_desc_sw128(stage, 2u * kAtomBytesStrm, 1024);
         constexpr int s0 = (MODE == ROW_PREDO) ? 3 : 1;     // g_dO' += P g_dV      | g_Q += dS g_dK
         constexpr int s1 = (MODE == ROW_PREDO) ? 2 : 0;     // g_dO' += (P o gdS) V | g_Q += g_S K
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
-            mma_ts(out, op_tmem(CF::kRB, ks), dm + moff(s0, ks), idesc_out, !(first && ks == 0));
+            mma_ts(out, op_tmem(CF::kRB + 128 * b, ks), dm + moff(s0, ks), idesc_out, !(first && ks == 0));
           _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
-            mma_ts(out, op_tmem(CF::kRB + 64, ks), dm + moff(s1, ks), idesc_out, 1);
+            mma_ts(out, op_tmem(CF::kRB + 128 * b + 64, ks), dm + moff(s1, ks), idesc_out, 1);
         }
         __syncwarp();
       };
@@ -320,7 +322,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           // ROW_Q keeps the pipe's order OUT(j-2), RB(j-1), RA(j): its second half-step is the long
           // one, and RA(j) queued any earlier delays the outputs that half-step waits behind.  The
           // scalar pass is faster with the two streams left to run freely (both measured).
-          if (MODE == ROW_Q && ok && j > 0) ok = mbar_wait(bar_rb_issued, (j - 1) & 1, abort_flag, t.status, wait_code(KIND, 13));
+          if (MODE == ROW_Q && LA == 1 && ok && j > 0) ok = mbar_wait(bar_rb_issued, (j - 1) & 1, abort_flag, t.status, wait_code(KIND, 13));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
@@ -329,28 +331,29 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           issue_ra_tail(stage);
         }
       } else {
-        // ---- second warp: RB products and outputs
-        ok = ok && wait_stream(0);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_rb_head(strm_base); issue_rb_tail(strm_base);
-          if (lane == 0) mbar_arrive(bar_rb_issued);
-        }
-        for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j % CF::kStages, nst = (j + 1) % CF::kStages;
-          const bool more = j + 1 < n_iter;
-          ok = mbar_wait(bar_op_full, j & 1, abort_flag, t.status, wait_code(KIND, 6));
-          if (ok && more) ok = wait_stream(j + 1);
+        // ---- second warp: RB products (LA tiles ahead) and outputs
+        for (int i = 0; i < LA && i < n_iter && ok; ++i) {
+          ok = wait_stream(i);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_out(strm_base + st * CF::kStageBytes, j == 0);
+          issue_rb(strm_base + (i % CF::kStages) * CF::kStageBytes, i % LA);
+          if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued);
+        }
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int st = j % CF::kStages, b = j % LA;
+          const int nj = j + LA;
+          ok = mbar_wait(bar_op_full(b), (j / LA) & 1, abort_flag, t.status, wait_code(KIND, 6));
+          if (ok && nj < n_iter) ok = wait_stream(nj);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_out(strm_base + st * CF::kStageBytes, j == 0, b);
           commit(bar_stream_empty(st));
-          if (more) {
-            const uint32_t nstage = strm_base + nst * CF::kStageBytes;
-            issue_rb_head(nstage); issue_rb_tail(nstage);
-            if (lane == 0) mbar_arrive(bar_rb_issued);
+          if (nj < n_iter) {
+            // buffer b again: after the outputs that read it, in this warp's own order
+            issue_rb(strm_base + (nj % CF::kStages) * CF::kStageBytes, b);
+            if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued);
           }
         }
         if (ok) commit(bar_acc_done);
@@ -425,8 +428,9 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
     float2 p_[16], a_[16];   // carried from half-step 1 to half-step 2 (ROW_PREDO: a_ = p * gdS)
     float2 acc_D = zero2, acc_2 = zero2, acc_A = zero2, acc_E = zero2;   // ROW_PREDO row sums
-    const uint32_t ra = lane_addr + CF::kRA, rb = lane_addr + CF::kRB;
+    const uint32_t ra = lane_addr + CF::kRA;
     for (int it = 0; it < n_iter && ok; ++it) {
+      const uint32_t rb = lane_addr + CF::kRB + 128u * (uint32_t)(it % LA);
       const int j0 = (t_begin + it) * BN;
       const int first = j0 + half * 32;
       const bool masked = !(first >= vlo && first + 31 < vhi);
@@ -475,7 +479,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       }
 
       // ---------------- half-step 2: RB ------------------------------------------
-      ok = mbar_wait(bar_rb_full, it & 1, abort_flag, t.status, wait_code(KIND, 8));
+      ok = mbar_wait(bar_rb_full(it % LA), (it / LA) & 1, abort_flag, t.status, wait_code(KIND, 8));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
@@ -514,7 +518,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_op_full);
+      if (lane == 0) mbar_arrive(bar_op_full(it % LA));
     }
 
     // ---------------- results ------------------------------------------------------
