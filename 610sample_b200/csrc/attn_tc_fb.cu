@@ -375,16 +375,20 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
 
     // BWD_COL: per-query scalars of a streamed tile, fetched one tile ahead by the first four warps
     // (thread -> (which, query)) and handed over in shared memory; every warp arrives on the barrier.
+    // The load is issued a tile ahead and its value is only touched when it is published, so that
+    // its latency never stalls the warp.
     auto fetch_stat = [&](int tile_it) {
       const int which = (threadIdx.x >> 6) & 1, c = threadIdx.x & 63;
       const int qi = (t_begin + tile_it) * BN + c;
-      float v = (which == 0) ? -INFINITY : 0.f;
+      float raw = (which == 0) ? INFINITY : 0.f;      // beyond N_q: L = +inf (p = 0), Dv = 0
       if (CF::kCol && threadIdx.x < 128 && tile_it < n_iter && qi < g.N_q)
-        v = (which == 0) ? -__ldg(t.L + row_off + qi) * kLog2e : -__ldg(t.Dv + row_off + qi);
-      return v;
+        raw = (which == 0) ? __ldg(t.L + row_off + qi) : __ldg(t.Dv + row_off + qi);
+      return raw;
     };
-    auto publish_stat = [&](int tile_it, float v) {
-      if (threadIdx.x < 128) aux_f[(tile_it & 1) * 128 + (threadIdx.x >> 6) * 64 + (threadIdx.x & 63)] = v;
+    auto publish_stat = [&](int tile_it, float raw) {
+      const int which = (threadIdx.x >> 6) & 1;
+      if (threadIdx.x < 128)
+        aux_f[(tile_it & 1) * 128 + which * 64 + (threadIdx.x & 63)] = (which == 0) ? -raw * kLog2e : -raw;
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->stats_ready[tile_it & 1]));
     };

@@ -374,18 +374,21 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     // Thread (which, c) fetches one of them; the values of tile it+1 are fetched during tile it and
     // published at its end, so that neither the global loads nor the hand-over are waited for.
     const int which = threadIdx.x >> 6, qc = threadIdx.x & 63;
+    // The loads are issued a tile ahead and their values are only touched when they are
+    // published, so that their latency never stalls the warp.
     auto fetch_stat = [&](int tile_it) {
       const int qi = (t_begin + tile_it) * BN + qc;
-      float v = (which == 0) ? -INFINITY : 0.f;
+      float3 raw = make_float3((which == 0) ? INFINITY : 0.f, 0.f, 0.f);   // beyond N_q: L = +inf (p = 0), the rest 0
       if (tile_it < n_iter && qi < g.N_q) {
-        if (which == 0) v = -__ldg(t.L + row_off + qi) * kLog2e;
-        else if (which == 1) v = -__ldg(t.dot2 + row_off + qi);
-        else if (which == 2) v = -__ldg(t.Dv + row_off + qi);
-        else v = -fmaf(__ldg(t.dot2 + row_off + qi), __ldg(t.Dv + row_off + qi), __ldg(t.dot3 + row_off + qi));
+        if (which == 0) raw.x = __ldg(t.L + row_off + qi);
+        else if (which == 1) raw.x = __ldg(t.dot2 + row_off + qi);
+        else if (which == 2) raw.x = __ldg(t.Dv + row_off + qi);
+        else { raw.x = __ldg(t.dot2 + row_off + qi); raw.y = __ldg(t.Dv + row_off + qi); raw.z = __ldg(t.dot3 + row_off + qi); }
       }
-      return v;
+      return raw;
     };
-    auto publish_stat = [&](int tile_it, float v) {
+    auto publish_stat = [&](int tile_it, float3 raw) {
+      const float v = (which == 0) ? -raw.x * kLog2e : (which == 3) ? -fmaf(raw.x, raw.y, raw.z) : -raw.x;
       col_stats[(tile_it & 1) * 256 + which * 64 + qc] = v;
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->stats_ready[tile_it & 1]));
@@ -394,7 +397,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
     for (int it = 0; it < n_iter; ++it) {
       const int j0 = (t_begin + it) * BN;
       const float* cs = col_stats + (it & 1) * 256;
-      const float next_stat = fetch_stat(it + 1);
+      const float3 next_stat = fetch_stat(it + 1);
       ok = mbar_wait(smem_u32(&ctl->stats_ready[it & 1]), (it >> 1) & 1, abort_flag, t.status, wait_code(KIND, 9));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
