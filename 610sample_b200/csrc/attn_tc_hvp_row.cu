@@ -28,8 +28,9 @@
 // elected lane inside a single branch: the first warp the RA products of every tile, the second
 // the outputs of a tile followed by the RB products of the next (so RB is overwritten only after
 // the outputs that read it).  With one issuing warp the latency of each of its waits (about 150
-// clocks even when satisfied) fell on an empty tensor pipe.  The result tile leaves through
-// shared memory and a TMA store, which clips rows and columns beyond the tensor.
+// clocks even when satisfied) fell on an empty tensor pipe.  At D = 64 tensor memory has room for
+// a second RB region and the RB products run a tile ahead of the outputs.  The result tile leaves
+// through shared memory and a TMA store, which clips rows and columns beyond the tensor.
 // Formulas: reference csrc/flash_double_backward_v7.cu:1257-1454.
 #include "attn_launch.h"
 #include "tc_common.cuh"
