@@ -49,8 +49,9 @@ struct RowControl {
   uint64_t stat_full;          // g_dQ tile in shared memory
   uint64_t staging_full;       // Q and dO tiles in the staging buffer (the last stage)
   uint64_t stat_tmem_ready;    // Q and dO copied to tensor memory
-  uint64_t stream_full[kRowMaxStages];
-  uint64_t stream_empty[kRowMaxStages];
+  // a stage has two halves with their own barriers: [K, g_dK] (index 0) and [V, g_dV] (index 1)
+  uint64_t stream_full[2][kRowMaxStages];
+  uint64_t stream_empty[2][kRowMaxStages];
   uint64_t ra_full;
   uint64_t ra_free;
   uint64_t rb_full[2];         // per RB buffer
@@ -61,7 +62,7 @@ struct RowControl {
   volatile uint32_t abort_flag;
 };
 
-static_assert(sizeof(RowControl) <= 256, "control block larger than its slot");
+static_assert(sizeof(RowControl) <= 512, "control block larger than its slot");
 
 template <int D>
 struct RowCfg {
@@ -75,7 +76,7 @@ struct RowCfg {
   static constexpr uint32_t kStatBytes = kAtoms * kAtomBytesStat;            // g_dQ only
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
   static_assert(kStageBytes == 2 * kAtoms * kAtomBytesStat, "Q and dO are staged in one stream stage");
-  static constexpr uint32_t kAuxBytes = 256;          // control block
+  static constexpr uint32_t kAuxBytes = 512;          // control block
   static constexpr uint32_t kContentBytes = kStatBytes + kStages * kStageBytes + kAuxBytes;
   static constexpr uint32_t kMaxSmem = 232448;
   static_assert(kContentBytes <= kMaxSmem, "shared memory over-subscribed");
@@ -146,16 +147,18 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   const uint32_t bar_acc_done = smem_u32(&ctl->acc_done);
   constexpr int LA = CF::kRbBufs;     // tiles the RB products run ahead of the outputs
   const uint32_t bar_rb_issued = smem_u32(&ctl->rb_issued);
-  auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
-  auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
+  auto bar_stream_full = [&](int h, int s) { return smem_u32(&ctl->stream_full[h][s]); };
+  auto bar_stream_empty = [&](int h, int s) { return smem_u32(&ctl->stream_empty[h][s]); };
 
   if (threadIdx.x == 0) {
     mbar_init(bar_stat_full, 1);
     mbar_init(bar_staging_full, 1);
     mbar_init(bar_stat_tmem_ready, kMathWarps);
     for (int s = 0; s < CF::kStages; ++s) {
-      mbar_init(bar_stream_full(s), 1);
-      mbar_init(bar_stream_empty(s), 1);
+      for (int h = 0; h < 2; ++h) {
+        mbar_init(bar_stream_full(h, s), 1);
+        mbar_init(bar_stream_empty(h, s), 1);
+      }
     }
     mbar_init(bar_ra_full, 1);
     mbar_init(bar_ra_free, kMathWarps);
@@ -183,13 +186,14 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         for (int h = 0; h < 2; ++h)
           tma_load_3d(staging + (x * kAtoms + a) * kAtomBytesStat + h * kAtomBytesStrm, &maps.m[x == 0 ? T_Q : T_dO],
                       a * 64, r0 + h * 64, bh, bar_staging_full);
-    mbar_arrive_expect_tx(bar_stream_full(0), CF::kStageBytes);
+    mbar_arrive_expect_tx(bar_stream_full(0, 0), CF::kStageBytes / 2);
+    mbar_arrive_expect_tx(bar_stream_full(1, 0), CF::kStageBytes / 2);
 #pragma unroll
     for (int sl = 0; sl < CF::kNStream; ++sl)
 #pragma unroll
       for (int a = 0; a < kAtoms; ++a)
         tma_load_3d(strm_base + CF::stream_off(sl, a), &maps.m[CF::stream_tensor(sl)], a * 64, t_begin * BN, bh,
-                    bar_stream_full(0));
+                    bar_stream_full(sl >> 1, 0));
     mbar_arrive_expect_tx(bar_stat_full, CF::kStatBytes);
 #pragma unroll
     for (int a = 0; a < kAtoms; ++a)
@@ -211,20 +215,29 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   if (warp == kProducerWarp) {
     if (lane == 0 && n_iter > 0) {
       bool ok = true;
+      // The two halves of a stage are released at different times: [K, g_dK] is last read by the
+      // RA products in the scalar pass (long before the outputs of the tile), [V, g_dV] by the RB
+      // products in the g_Q pass.  Each half is requested as soon as its own buffer is free, so the
+      // loads the first issuing warp waits for leave a tile earlier than a whole-stage release would
+      // allow (a load takes about as long as a tile).
       for (int it = 1; it < n_iter; ++it) {     // tile 0 was requested above
         const int st = it % CF::kStages;
-        ok = mbar_wait(bar_stream_empty(st), ((it / CF::kStages) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
-        // the last stage doubles as the staging buffer of Q and dO until they are in tensor memory
-        if (ok && it == CF::kStages - 1) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 10));
-        if (!ok) break;
-        mbar_arrive_expect_tx(bar_stream_full(st), CF::kStageBytes);
         const uint32_t stage = strm_base + st * CF::kStageBytes;
 #pragma unroll
-        for (int s = 0; s < CF::kNStream; ++s)
+        for (int h = 0; h < 2; ++h) {
+          ok = mbar_wait(bar_stream_empty(h, st), ((it / CF::kStages) & 1) ^ 1, abort_flag, t.status, wait_code(KIND, 1));
+          // the last stage doubles as the staging buffer of Q and dO until they are in tensor memory
+          if (ok && it == CF::kStages - 1) ok = mbar_wait(bar_stat_tmem_ready, 0, abort_flag, t.status, wait_code(KIND, 10));
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_stream_full(h, st), CF::kStageBytes / 2);
 #pragma unroll
-          for (int a = 0; a < kAtoms; ++a)
-            tma_load_3d(stage + CF::stream_off(s, a), &maps.m[CF::stream_tensor(s)], a * 64,
-                        (t_begin + it) * BN, bh, bar_stream_full(st));
+          for (int s2 = 0; s2 < 2; ++s2)
+#pragma unroll
+            for (int a = 0; a < kAtoms; ++a)
+              tma_load_3d(stage + CF::stream_off(2 * h + s2, a), &maps.m[CF::stream_tensor(2 * h + s2)], a * 64,
+                          (t_begin + it) * BN, bh, bar_stream_full(h, st));
+        }
+        if (!ok) break;
       }
       if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
         const long long t0 = clock64();
@@ -263,23 +276,12 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
       // Every batch of products is issued by the elected lane inside one branch, with the
       // descriptor of the stage built once: the instruction stream between two MMAs is an add.
-      // The last kTail k-steps of a score batch are issued after the wait that follows the batch
-      // in program order: the wait's latency then falls while the tensor pipe still has work queued.
-      constexpr int kTail = (D == 128) ? 2 : 0;
-      auto issue_ra_head = [&](uint32_t stage, int tr_tile) {
+      auto issue_ra = [&](uint32_t stage) {           // ends with the commit of the batch
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
             if (ks < ks_n) mma_ts(ra, qt + 8 * ks, dk + koff(0, ks), kIdesc128, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)
-            if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
-        }
-        __syncwarp();
-      };
-      auto issue_ra_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
-        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
-        if (elect_one()) {
-          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
+          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
             if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
           mma_commit(bar_ra_full);
         }
@@ -312,13 +314,15 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       // other are queued.  The tensor pipe needs no order between the two streams: RA(j+1) only
       // waits for RA(j) to have been read, and RB(j+1) follows OUT(j), which reads RB, in the
       // second warp's own order.
-      auto wait_stream = [&](int tile) {
-        return mbar_wait(bar_stream_full(tile % CF::kStages), (tile / CF::kStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
+      auto wait_stream = [&](int h, int tile) {   // half h of the stage of `tile` has landed
+        return mbar_wait(bar_stream_full(h, tile % CF::kStages), (tile / CF::kStages) & 1, abort_flag, t.status, wait_code(KIND, 3));
       };
+      // which issuing warp releases which half: the one whose products read it last
+      constexpr bool kRaReleasesKG = (MODE == ROW_PREDO);   // scalar pass: the outputs read V, g_dV only
       if (warp == kRowMmaWarp) {
         // ---- first warp: the RA products of every tile
         for (int j = 0; j < n_iter && ok; ++j) {
-          ok = wait_stream(j);
+          ok = wait_stream(0, j);
           if (ok && j > 0) ok = mbar_wait(bar_ra_free, (j - 1) & 1, abort_flag, t.status, wait_code(KIND, 4));
           // ROW_Q keeps the pipe's order OUT(j-2), RB(j-1), RA(j): its second half-step is the long
           // one, and RA(j) queued any earlier delays the outputs that half-step waits behind.  The
@@ -328,32 +332,34 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t stage = strm_base + (j % CF::kStages) * CF::kStageBytes;
-          issue_ra_head(stage, j);
-          issue_ra_tail(stage);
+          issue_ra(stage);
+          if (kRaReleasesKG) commit(bar_stream_empty(0, j % CF::kStages));
         }
       } else {
         // ---- second warp: RB products (LA tiles ahead) and outputs
         for (int i = 0; i < LA && i < n_iter && ok; ++i) {
-          ok = wait_stream(i);
+          ok = wait_stream(1, i);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
           issue_rb(strm_base + (i % CF::kStages) * CF::kStageBytes, i % LA);
+          if (!kRaReleasesKG) commit(bar_stream_empty(1, i % CF::kStages));
           if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued);
         }
         for (int j = 0; j < n_iter && ok; ++j) {
           const int st = j % CF::kStages, b = j % LA;
           const int nj = j + LA;
           ok = mbar_wait(bar_op_full(b), (j / LA) & 1, abort_flag, t.status, wait_code(KIND, 6));
-          if (ok && nj < n_iter) ok = wait_stream(nj);
+          if (ok && nj < n_iter) ok = wait_stream(1, nj);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
           issue_out(strm_base + st * CF::kStageBytes, j == 0, b);
-          commit(bar_stream_empty(st));
+          commit(bar_stream_empty(kRaReleasesKG ? 1 : 0, st));   // the half the outputs read
           if (nj < n_iter) {
             // buffer b again: after the outputs that read it, in this warp's own order
             issue_rb(strm_base + (nj % CF::kStages) * CF::kStageBytes, b);
+            if (!kRaReleasesKG) commit(bar_stream_empty(1, nj % CF::kStages));
             if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued);
           }
         }
