@@ -121,9 +121,14 @@ int run(int op, const attn_shape_t* s, attn::Tensors& t, void* stream, int phase
   if (g.N_q == 0 || g.N_kv == 0) return run_empty(op, s, t, static_cast<cudaStream_t>(stream));
   // Bind the device's primary context to this host thread.  Tensor-map encoding is a
   // driver call and fails with "invalid context" on a thread that has made no runtime
-  // call yet (e.g. a freshly started autograd worker thread).
-  cudaError_t e0 = cudaFree(nullptr);
-  if (e0 != cudaSuccess) return fail(ATTN_ECUDA, "cudaFree(0): %s", cudaGetErrorString(e0));
+  // call yet (e.g. a freshly started autograd worker thread).  cudaSetDevice on the current
+  // device does that and, unlike a null cudaFree, is legal while a stream is being captured.
+  {
+    int dev = 0;
+    cudaError_t e0 = cudaGetDevice(&dev);
+    if (e0 == cudaSuccess) e0 = cudaSetDevice(dev);
+    if (e0 != cudaSuccess) return fail(ATTN_ECUDA, "binding the device context: %s", cudaGetErrorString(e0));
+  }
   int rc = status_pointer(&t.status);
   if (rc != ATTN_OK) return rc;
   const bool use_tc = s->impl == ATTN_IMPL_TENSOR ||

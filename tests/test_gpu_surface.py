@@ -182,3 +182,37 @@ def test_empty_inputs(mods):
     none = torch.empty(0, 3, 8, 64, device=DEV, dtype=torch.bfloat16)
     O1, L1 = ac.v7_forward(none, none, none, 16, 0)
     assert O1.numel() == 0 and ac.last_launch_count() == 0
+
+
+def test_double_backward_under_cuda_graph_capture():
+    """The call is capturable: backward and double backward fork onto the library's helper stream
+    and join back, tensor maps travel as kernel parameters, nothing is allocated by the library.
+    The replayed graph must reproduce the eager results bit for bit."""
+    tcapi = importlib.import_module("610sample_b200.torch_capi")
+    capi = importlib.import_module("610sample_b200.capi")
+    inp = orc.make_inputs(1, 4, 512, 512, 128, seed=21, dtype=torch.bfloat16)
+    g = {n: t.to(DEV) for n, t in inp.items()}
+    O, L = tcapi.forward(g["Q"], g["K"], g["V"], 512, 0)
+    s = tcapi._shape(g["Q"], g["K"], 512, 0, 0, 0)
+    scratch = torch.empty(capi.lib().attn_b200_double_backward_scratch_bytes(s) // 4 + 4, dtype=torch.float32, device=DEV)
+    eager = tuple(torch.empty_like(g[n]) for n in ("Q", "Q", "K", "V"))
+    tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, 512, 0,
+                          scratch=scratch, out=eager)
+    torch.cuda.synchronize()
+    out = tuple(torch.zeros_like(t) for t in eager)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, 512, 0,
+                                  scratch=scratch, out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        for t in out:
+            t.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(eager, out):
+            assert torch.equal(a, b)
+    assert capi.device_status() == 0
