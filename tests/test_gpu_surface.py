@@ -216,3 +216,45 @@ def test_double_backward_under_cuda_graph_capture():
         for a, b in zip(eager, out):
             assert torch.equal(a, b)
     assert capi.device_status() == 0
+
+
+def test_two_host_threads_on_their_own_streams():
+    """Two host threads call the C ABI at the same time on different streams (ctypes drops the
+    GIL).  They share the device's helper stream and its fork / join events; each must still get
+    exactly the results of a serial call."""
+    import threading
+    tcapi = importlib.import_module("610sample_b200.torch_capi")
+    capi = importlib.import_module("610sample_b200.capi")
+    cases = []
+    for seed in (31, 32):
+        inp = orc.make_inputs(1, 8, 1024, 1024, 128, seed=seed, dtype=torch.bfloat16)
+        g = {n: t.to(DEV) for n, t in inp.items()}
+        O, L = tcapi.forward(g["Q"], g["K"], g["V"], 1024, 0)
+        ref = tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, 1024, 0)
+        cases.append((g, O, L, ref))
+    torch.cuda.synchronize()
+    results = [None, None]
+    errors = []
+
+    def work(i):
+        try:
+            g, O, L, _ = cases[i]
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for _ in range(20):
+                    r = tcapi.double_backward(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L, 1024, 0)
+            st.synchronize()
+            results[i] = r
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    th = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for x in th:
+        x.start()
+    for x in th:
+        x.join()
+    assert not errors, errors
+    for i in range(2):
+        for a, b in zip(cases[i][3], results[i]):
+            assert torch.equal(a, b)
+    assert capi.device_status() == 0
