@@ -235,23 +235,42 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
       // Every batch of products is issued by the elected lane inside one branch, with the
       // descriptor of the stage built once: the instruction stream between two MMAs is an add.
-      auto issue_ra = [&](uint32_t stage) {           // ends with the commit of the batch
+      // The last kTail k-steps of a score batch are issued after the wait that follows the batch
+      // in program order: the wait's latency then falls while the tensor pipe still has work queued.
+      constexpr int kTail = (D == 128) ? 2 : 0;
+      auto issue_ra_head = [&](uint32_t stage) {
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // [S^T | K g_dQ^T] = K [Q; g_dQ]^T
             if (ks < ks_n) mma_ss(ra, stat_desc(0, ks), dk + koff(0, ks), kIdesc128, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gdS^T += g_dK Q^T
+          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)   // gdS^T += g_dK Q^T
+            if (ks < ks_n) mma_ss(ra + 64, stat_desc(2, ks), dk + koff(0, ks), kIdesc64, 1);
+        }
+        __syncwarp();
+      };
+      auto issue_ra_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
             if (ks < ks_n) mma_ss(ra + 64, stat_desc(2, ks), dk + koff(0, ks), kIdesc64, 1);
           mma_commit(bar_ra_full);
         }
         __syncwarp();
       };
-      auto issue_rb = [&](uint32_t stage) {           // ends with the commit of the batch
+      auto issue_rb_head = [&](uint32_t stage) {
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // dP^T = V dO^T
             if (ks < ks_n) mma_ss(rb, stat_desc(1, ks), dk + koff(2, ks), kIdesc64, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)   // gPdV^T = g_dV dO^T
+          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)   // gPdV^T = g_dV dO^T
+            if (ks < ks_n) mma_ss(rb + 64, stat_desc(3, ks), dk + koff(2, ks), kIdesc64, ks > 0);
+        }
+        __syncwarp();
+      };
+      auto issue_rb_tail = [&](uint32_t stage) {      // ends with the commit of the whole batch
+        const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
             if (ks < ks_n) mma_ss(rb + 64, stat_desc(3, ks), dk + koff(2, ks), kIdesc64, ks > 0);
           mma_commit(bar_rb_full);
         }
@@ -295,7 +314,8 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t stage = strm_base + (j % CF::kStages) * CF::kStageBytes;
-          issue_ra(stage);
+          issue_ra_head(stage);
+          issue_ra_tail(stage);
         }
       } else {
         // ---- second warp: RB products and outputs
@@ -303,7 +323,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
           tc_fence_after_sync();
-          issue_rb(strm_base);
+          issue_rb_head(strm_base); issue_rb_tail(strm_base);
         }
         for (int j = 0; j < n_iter && ok; ++j) {
           const int st = j % CF::kStages, nst = (j + 1) % CF::kStages;
@@ -322,7 +342,7 @@ hvp_col_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           commit(bar_stream_empty(st));
           if (more) {
             const uint32_t nstage = strm_base + nst * CF::kStageBytes;
-            issue_rb(nstage);
+            issue_rb_head(nstage); issue_rb_tail(nstage);
             }
         }
         if (ok) commit(bar_acc_done);

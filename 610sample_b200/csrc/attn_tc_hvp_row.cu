@@ -276,12 +276,21 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
 
       // Every batch of products is issued by the elected lane inside one branch, with the
       // descriptor of the stage built once: the instruction stream between two MMAs is an add.
+      // The RA batch goes out in two elected branches, the last kTail k-steps and the commit in the
+      // second: measured, the scalar pass loses 10 % when the whole batch is issued in one branch
+      // (the short gap lets the other issuing warp's products into the queue in between).
+      constexpr int kTail = (D == 128) ? 2 : 0;
       auto issue_ra = [&](uint32_t stage) {           // ends with the commit of the batch
         const uint64_t dk = smem_desc_sw128(stage, 16, 1024);
         if (elect_one()) {
           _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
             if (ks < ks_n) mma_ts(ra, qt + 8 * ks, dk + koff(0, ks), kIdesc128, ks > 0);
-          _Pragma("unroll") for (int ks = 0; ks < KS; ++ks)
+          _Pragma("unroll") for (int ks = 0; ks < KS - kTail; ++ks)
+            if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
+        }
+        __syncwarp();
+        if (elect_one()) {
+          _Pragma("unroll") for (int ks = KS - kTail; ks < KS; ++ks)
             if (ks < ks_n) mma_ss(ra + 64, gq_desc(ks), dk + koff(0, ks), kIdesc64, 1);
           mma_commit(bar_ra_full);
         }
