@@ -47,7 +47,7 @@ COL_KERNEL_GEMMS = 8
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture at 16 (batch, head)
 # slices (profiles/hvp_kernels_bf16_causal_N4096_D128_16heads_ncu_full.md); traffic grows in
 # proportion to the number of slices, so the bench scales it by BH / 16.
-NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 196.6e6, "row": 171.2e6, "col": 138.4e6}
+NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 199.9e6, "row": 172.7e6, "col": 138.0e6}
 
 
 def visible_pairs_causal(n: int) -> int:
