@@ -11,6 +11,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <cstdio>
+#include <mutex>
 #include <vector>
 
 #include "attn_b200.h"
@@ -72,12 +74,48 @@ void check_rc(int rc, const char* what) {
   TORCH_CHECK(rc == ATTN_OK, what, " failed (", rc, "): ", attn_b200_last_error());
 }
 
+// A kernel that gives up on a bounded wait stores a code in the device's status word and returns;
+// its outputs are then meaningless.  Each call of this module ends by enqueueing a copy of that
+// word into a page-locked host word of the device, and begins by looking at the host word: a
+// time-out of an earlier call is reported, without any synchronisation on the good path, as an
+// exception of the first call that starts after the copy has landed.
+struct StatusMirror {
+  torch::Tensor word;   // one int32 in page-locked host memory
+};
+
+uint32_t* status_mirror(int device) {
+  static StatusMirror mirrors[64];
+  static std::mutex mu;
+  TORCH_CHECK(device >= 0 && device < 64, "device index out of range");
+  std::lock_guard<std::mutex> lock(mu);
+  if (!mirrors[device].word.defined())
+    mirrors[device].word = torch::zeros({1}, torch::dtype(torch::kInt32).pinned_memory(true));
+  return reinterpret_cast<uint32_t*>(mirrors[device].word.data_ptr<int32_t>());
+}
+
+void raise_if_earlier_call_timed_out(int device) {
+  volatile uint32_t* w = status_mirror(device);
+  if (*w == 0u) return;
+  *w = 0u;
+  uint32_t code = 0;
+  int rc = attn_b200_device_status(&code);     // synchronises, reads and clears the device word
+  char hex[16];
+  snprintf(hex, sizeof(hex), "0x%x", code);
+  TORCH_CHECK(rc == ATTN_OK && code == 0u, "an earlier attention kernel on this device gave up on a bounded wait (status ",
+              hex, "); its outputs are invalid");
+}
+
+void poll_status(int device, cudaStream_t stream) {
+  check_rc(attn_b200_status_poll_async(status_mirror(device), stream), "attn_b200_status_poll_async");
+}
+
 }  // namespace
 
 std::vector<torch::Tensor> v7_forward_cuda(torch::Tensor Q, torch::Tensor K, torch::Tensor V, int window_size,
                                            int chunk_id, int mask_mode, int impl) {
   check_qkv(Q, K, V);
   c10::cuda::CUDAGuard guard(Q.device());
+  raise_if_earlier_call_timed_out(Q.device().index());
   Q = dense(Q); K = dense(K); V = dense(V);
   attn_shape_t s = make_shape(Q, K, window_size, chunk_id, mask_mode, impl);
   auto O = torch::empty_like(Q);
@@ -85,6 +123,7 @@ std::vector<torch::Tensor> v7_forward_cuda(torch::Tensor Q, torch::Tensor K, tor
   check_rc(attn_b200_forward(&s, Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr<float>(),
                              at::cuda::getCurrentCUDAStream().stream()),
            "v7_forward");
+  poll_status(Q.device().index(), at::cuda::getCurrentCUDAStream().stream());
   return {O, L};
 }
 
@@ -97,6 +136,7 @@ std::vector<torch::Tensor> v7_backward_cuda(torch::Tensor dO, torch::Tensor Q, t
   TORCH_CHECK(L.is_cuda() && L.scalar_type() == at::kFloat && L.numel() == Q.size(0) * Q.size(1) * Q.size(2),
               "L must be a float32 CUDA tensor of shape [B, H, N_q]");
   c10::cuda::CUDAGuard guard(Q.device());
+  raise_if_earlier_call_timed_out(Q.device().index());
   dO = dense(dO); Q = dense(Q); K = dense(K); V = dense(V); O = dense(O); L = L.contiguous();
   attn_shape_t s = make_shape(Q, K, window_size, chunk_id, mask_mode, impl);
   auto dQ = torch::empty_like(Q);
@@ -108,6 +148,7 @@ std::vector<torch::Tensor> v7_backward_cuda(torch::Tensor dO, torch::Tensor Q, t
                               L.data_ptr<float>(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(),
                               scratch.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
            "v7_backward");
+  poll_status(Q.device().index(), at::cuda::getCurrentCUDAStream().stream());
   return {dQ, dK, dV};
 }
 
@@ -123,6 +164,7 @@ std::vector<torch::Tensor> v7_double_backward_cuda(torch::Tensor g_dQ, torch::Te
   TORCH_CHECK(L.is_cuda() && L.scalar_type() == at::kFloat && L.numel() == Q.size(0) * Q.size(1) * Q.size(2),
               "L must be a float32 CUDA tensor of shape [B, H, N_q]");
   c10::cuda::CUDAGuard guard(Q.device());
+  raise_if_earlier_call_timed_out(Q.device().index());
   g_dQ = dense(g_dQ); g_dK = dense(g_dK); g_dV = dense(g_dV);
   dO = dense(dO); Q = dense(Q); K = dense(K); V = dense(V); L = L.contiguous();
   attn_shape_t s = make_shape(Q, K, window_size, chunk_id, mask_mode, impl);
@@ -139,6 +181,7 @@ std::vector<torch::Tensor> v7_double_backward_cuda(torch::Tensor g_dQ, torch::Te
                                      g_dO.data_ptr(), g_Q.data_ptr(), g_K.data_ptr(), g_V.data_ptr(),
                                      scratch.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
            "v7_double_backward");
+  poll_status(Q.device().index(), at::cuda::getCurrentCUDAStream().stream());
   return {g_dO, g_Q, g_K, g_V};
 }
 

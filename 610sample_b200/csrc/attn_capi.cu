@@ -351,6 +351,16 @@ int attn_b200_device_status(uint32_t* code) {
   return ATTN_OK;
 }
 
+int attn_b200_status_poll_async(uint32_t* host_word, void* stream) {
+  if (host_word == nullptr) return fail(ATTN_EINVAL, "host_word is null");
+  unsigned int* p = nullptr;
+  int rc = status_pointer(&p);
+  if (rc != ATTN_OK) return rc;
+  cudaError_t e = cudaMemcpyAsync(host_word, p, sizeof(uint32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaMemcpyAsync(status word): %s", cudaGetErrorString(e));
+  return ATTN_OK;
+}
+
 const char* attn_b200_last_error(void) { return tl_error; }
 
 const char* attn_b200_version(void) { return "attn_b200 0.1 (sm_100a)"; }

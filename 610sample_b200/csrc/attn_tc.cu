@@ -50,6 +50,7 @@ selftest_gemm_kernel(const __grid_constant__ SelftestMaps maps, const T* __restr
   Control* ctl = reinterpret_cast<Control*>(gen + 4 * 16384);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool b_mn = (flags & 1) != 0, a_manual = (flags & 2) != 0, a_tmem = (flags & 4) != 0;
+  const bool timeout_test = (flags & 8) != 0;
   const uint32_t bar_full = smem_u32(&ctl->stat_full), bar_done = smem_u32(&ctl->acc_done);
   if (threadIdx.x == 0) {
     mbar_init(bar_full, 1);
@@ -92,6 +93,13 @@ selftest_gemm_kernel(const __grid_constant__ SelftestMaps maps, const T* __restr
   __syncthreads();
 
   const int ka = K / 64;
+  if (timeout_test) {
+    // Exercise of the time-out path: thread 0 waits, with a limit of about a millisecond, on a
+    // barrier nothing will ever arrive on.  It stores its code in the status word and raises the
+    // abort flag; the other threads leave their wait below through that flag, and everybody goes
+    // through the common teardown, which frees the tensor memory.  Nothing is computed.
+    if (threadIdx.x == 0) (void)mbar_wait_limit(bar_full, 0, abort_flag, status, 0x7003u, 1000000LL);
+  } else
   if (threadIdx.x == 0) {
     uint32_t bytes = 0;
     const bool a_tma = !a_manual && !a_tmem;
@@ -236,9 +244,13 @@ cudaError_t launch_fwd_bwd(int kind, int D, int is_bf16, const TmaMaps& maps, co
 // Kernels of one operation that do not depend on one another (g_Q and g_K/g_V of the double
 // backward; dQ and dK/dV of the backward) run side by side: the second is launched on a helper
 // stream of the device between an event fork and an event join on the caller's stream, so the
-// SMs that one kernel's last CTAs leave idle take CTAs of the other.  The pattern is legal under
-// stream capture.  One helper stream and two events per device, created on first use; when that
-// fails the launches stay on the caller's stream.
+// SMs that one kernel's last CTAs leave idle take CTAs of the other.  One helper stream and two
+// events per device, created on first use and shared by every caller stream and host thread (the
+// mutex covers one fork ... join enqueue).  A stream that is being captured is never forked: a
+// capture would pull the shared helper stream into the graph until the capture ends, long after
+// the mutex is released, and an eager call of another thread in that window would either
+// invalidate the capture or be merged into it.  Under capture, and whenever the helper cannot be
+// had, both launches stay on the caller's stream.
 struct Helper {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
@@ -268,6 +280,15 @@ static Helper* helper_for_current_device() {
 // first(s) and second(helper stream) between fork and join; serial on s without a helper
 template <typename F1, typename F2>
 static cudaError_t run_side_by_side(cudaStream_t s, bool allow_helper, F1 first, F2 second) {
+  if (allow_helper) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) {   // e.g. the legacy stream while another stream captures
+      (void)cudaGetLastError();
+      allow_helper = false;
+    } else if (cap != cudaStreamCaptureStatusNone) {
+      allow_helper = false;
+    }
+  }
   Helper* h = allow_helper ? helper_for_current_device() : nullptr;
   if (h == nullptr) {
     cudaError_t e = first(s);

@@ -57,7 +57,11 @@ struct RowControl {
   uint64_t rb_full[2];         // per RB buffer
   uint64_t op_full[2];         // per RB buffer: operands of a tile written
   uint64_t acc_done;
-  uint64_t rb_issued;          // second issuing warp -> first: the RB products of a tile are queued
+  // second issuing warp -> first: the RB products of a tile are queued.  Two barriers used in
+  // turn (tile parity): the first warp may fall a whole tile behind the second (it also waits for
+  // the [K, g_dK] load), and a single barrier completing twice before it is looked at would show
+  // the waited-for parity as pending again.
+  uint64_t rb_issued[2];
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
@@ -146,7 +150,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
   auto bar_op_full = [&](int b) { return smem_u32(&ctl->op_full[b]); };
   const uint32_t bar_acc_done = smem_u32(&ctl->acc_done);
   constexpr int LA = CF::kRbBufs;     // tiles the RB products run ahead of the outputs
-  const uint32_t bar_rb_issued = smem_u32(&ctl->rb_issued);
+  auto bar_rb_issued = [&](int tile) { return smem_u32(&ctl->rb_issued[tile & 1]); };
   auto bar_stream_full = [&](int h, int s) { return smem_u32(&ctl->stream_full[h][s]); };
   auto bar_stream_empty = [&](int h, int s) { return smem_u32(&ctl->stream_empty[h][s]); };
 
@@ -167,7 +171,8 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
       mbar_init(bar_op_full(b), kMathWarps);
     }
     mbar_init(bar_acc_done, 1);
-    mbar_init(bar_rb_issued, 1);
+    mbar_init(bar_rb_issued(0), 1);
+    mbar_init(bar_rb_issued(1), 1);
     ctl->abort_flag = 0u;
     ctl->tmem_base = 0u;
     fence_barrier_init();
@@ -336,7 +341,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           // ROW_Q keeps the pipe's order OUT(j-2), RB(j-1), RA(j): its second half-step is the long
           // one, and RA(j) queued any earlier delays the outputs that half-step waits behind.  The
           // scalar pass is faster with the two streams left to run freely (both measured).
-          if (MODE == ROW_Q && LA == 1 && ok && j > 0) ok = mbar_wait(bar_rb_issued, (j - 1) & 1, abort_flag, t.status, wait_code(KIND, 13));
+          if (MODE == ROW_Q && LA == 1 && ok && j > 0) ok = mbar_wait(bar_rb_issued(j - 1), ((j - 1) >> 1) & 1, abort_flag, t.status, wait_code(KIND, 13));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
@@ -353,7 +358,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
           tc_fence_after_sync();
           issue_rb(strm_base + (i % CF::kStages) * CF::kStageBytes, i % LA);
           if (!kRaReleasesKG) commit(bar_stream_empty(1, i % CF::kStages));
-          if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued);
+          if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued(i));
         }
         for (int j = 0; j < n_iter && ok; ++j) {
           const int st = j % CF::kStages, b = j % LA;
@@ -369,7 +374,7 @@ hvp_row_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Ten
             // buffer b again: after the outputs that read it, in this warp's own order
             issue_rb(strm_base + (nj % CF::kStages) * CF::kStageBytes, b);
             if (!kRaReleasesKG) commit(bar_stream_empty(1, nj % CF::kStages));
-            if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued);
+            if (LA == 1 && lane == 0) mbar_arrive(bar_rb_issued(nj));
           }
         }
         if (ok) commit(bar_acc_done);

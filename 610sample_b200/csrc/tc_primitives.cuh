@@ -50,19 +50,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // roles see the flag in their own waits and leave as well.
 constexpr long long kWaitLimitCycles = 4000000000LL;
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          unsigned int* status, uint32_t code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                unsigned int* status, uint32_t code, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0u) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1u;
       if (status != nullptr) atomicCAS(status, 0u, code);
       return false;
     }
   }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          unsigned int* status, uint32_t code) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, code, kWaitLimitCycles);
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -185,6 +190,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
 //   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format (0 f16, 1 bf16)
 //   [15] A major   [16] B major (0 = K-major, 1 = MN-major)
 //   [17,23) N >> 3             [24,29) M >> 4
+// A and B have to be given the same format: on this hardware an instruction whose descriptor
+// names f16 for A and bf16 for B raises "illegal instruction".
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int is_bf16, int a_mn_major,
                                                   int b_mn_major) {
   return (1u << 4) | ((uint32_t)is_bf16 << 7) | ((uint32_t)is_bf16 << 10) |

@@ -188,14 +188,16 @@ def run_ours(args):
     tcapi = importlib.import_module("610sample_b200.torch_capi")
     capi = importlib.import_module("610sample_b200.capi")
 
+    sharding = importlib.import_module("610sample_b200.sharding")
+
     w = WORKLOAD
     BH = args.bh if args.bh > 0 else w["B"] * w["H"]
-    assert BH % world == 0, "batch*heads must divide over the ranks"
-    bh_local = BH // world
     N, D = w["N"], w["D"]
-    # every rank draws the full seeded workload and keeps its contiguous slice of (batch, head)
+    # every rank draws the full seeded workload and keeps its contiguous range of (batch, head) slices
     full = orc.make_inputs(1, BH, N, N, D, seed=0, dtype=torch.bfloat16)
-    sl = slice(rank * bh_local, (rank + 1) * bh_local)
+    begin, end = sharding.shard_range(BH, world, rank)
+    bh_local = end - begin
+    sl = slice(begin, end)
     host = {n: full[n][:, sl].contiguous().pin_memory() for n in orc.INPUT_NAMES}
     del full
     g = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
@@ -218,16 +220,17 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the clock sampler runs from before the warm-up, so that short timed regions still get samples
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     launches_per_step = capi.lib().attn_b200_last_launch_count()
     torch.cuda.synchronize()
 
     # ---- kernel-resident timing ------------------------------------------------
-    sampler = ClockSampler(local)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
-    sampler.start()
     for a, b in ev:
         flush.zero_()
         a.record()
@@ -236,10 +239,7 @@ def run_ours(args):
     barrier()
     clocks = sampler.stop()
     ms = sum(a.elapsed_time(b) for a, b in ev)
-    tm = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-    ms_per_step = float(tm.item()) / args.steps
+    ms_per_step = sharding.max_over_ranks(ms, dev) / args.steps
 
     # ---- per-kernel timing of the dominant kernel (rank 0, single-GPU roofline) --
     phase_ms = {}
@@ -258,6 +258,46 @@ def run_ours(args):
                 tot += a.elapsed_time(b)
             phase_ms[name] = tot / reps
 
+    # ---- forward and first backward at the same shape (rank-local slices) ----------
+    def time_call(fn, reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        tot = 0.0
+        for _ in range(reps):
+            flush.zero_()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            tot += a.elapsed_time(b)
+        return tot / reps
+
+    bwd_scratch = torch.empty(capi.lib().attn_b200_backward_scratch_bytes(s) // 4 + 4, dtype=torch.float32, device=dev)
+    fb_reps = max(3, min(args.steps, 10))
+    fwd_fn = lambda: tcapi.forward(g["Q"], g["K"], g["V"], ws, cid, mm)
+    bwd_fn = lambda: tcapi.backward(g["dO"], g["Q"], g["K"], g["V"], O, L, ws, cid, mm, scratch=bwd_scratch)
+    for _ in range(2):
+        fwd_fn(); bwd_fn()
+    fwd_ms = sharding.max_over_ranks(time_call(fwd_fn, fb_reps), dev)
+    bwd_ms = sharding.max_over_ranks(time_call(bwd_fn, fb_reps), dev)
+
+    # ---- the same step looped for >= 2 s: the board's power cap pulls the SM clock down ----
+    sustained = None
+    if not args.no_sustained:
+        n_sus = max(20, int(2000.0 / max(ms_per_step, 1e-3)) + 1)
+        sus_sampler = ClockSampler(local)
+        barrier()
+        sus_sampler.start()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_sus):
+            step()                       # no L2 flush: the inputs of a step (806 MB) exceed the 126 MB L2
+        b.record()
+        barrier()
+        sus_clocks = sus_sampler.stop()
+        sus_ms = sharding.max_over_ranks(a.elapsed_time(b), dev) / n_sus
+        sustained = {"steps": n_sus, "ms_per_step": sus_ms, "clocks": sus_clocks,
+                     "l2": "no flush between steps; the step's inputs exceed L2"}
+
     # ---- end to end through the plugin call, host buffers ------------------------
     e2e_steps = max(1, min(args.steps, 5))
     in_names = ("g_dQ", "g_dK", "g_dV", "dO", "Q", "K", "V")
@@ -268,15 +308,16 @@ def run_ours(args):
     # The (batch, head) slices are independent, so the host-buffer path is pipelined over
     # chunks of slices on three streams: upload of chunk c+1, kernels of chunk c and download
     # of chunk c-1 overlap (PCIe is full duplex).  Every byte still crosses inside the timed region.
-    n_chunks = args.e2e_chunks if (args.e2e_chunks > 0 and bh_local % args.e2e_chunks == 0) else 1
-    per = bh_local // n_chunks
+    # at most one chunk per slice; chunk sizes differ by at most one
+    n_chunks = max(1, min(args.e2e_chunks, bh_local))
+    chunk_bounds = [sharding.shard_range(bh_local, n_chunks, c) for c in range(n_chunks)]
     s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
 
     def e2e_step():
         main = torch.cuda.current_stream()
         s_in.wait_stream(main); s_cmp.wait_stream(main); s_out.wait_stream(main)
-        for c in range(n_chunks):
-            sl_c = slice(c * per, (c + 1) * per)
+        for c0, c1 in chunk_bounds:
+            sl_c = slice(c0, c1)
             with torch.cuda.stream(s_in):
                 d = {n: host[n][:, sl_c].to(dev, non_blocking=True) for n in in_names}
                 dO_ = host_O[:, sl_c].to(dev, non_blocking=True)
@@ -307,11 +348,20 @@ def run_ours(args):
             e2e_step()
         b.record()
     barrier()
-    te = torch.tensor([max(a.elapsed_time(b), 1e-9)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = float(te.item()) / e2e_steps
+    e2e_ms = sharding.max_over_ranks(max(a.elapsed_time(b), 1e-9), dev) / e2e_steps
     status = capi.device_status()
+
+    # ---- the caller: TTT meta-step (bench_ttt.py) on the same GPUs, NCCL all-reduce of the outer gradient
+    ttt = None
+    if not args.no_ttt:
+        torch.cuda.empty_cache()
+        import bench_ttt
+        ttt_line = bench_ttt.measure(argparse.Namespace(gpus=world, steps=3, warmup=1, impl="ours", small=False),
+                                     init_process_group=False)
+        if ttt_line is not None:
+            ttt = {k: ttt_line[k] for k in ("value", "unit", "ms_per_step", "steps", "warmup", "scaling",
+                                            "attention_ms_per_step", "attention_share", "peak_memory_mb")}
+            ttt["workload"] = ttt_line["config"]["workload"]
 
     flops_step = 2.0 * D * HVP_GEMMS * visible_pairs_causal(N) * BH          # whole job, all ranks
     value = flops_step / (ms_per_step * 1e-3) / 1e12
@@ -324,18 +374,32 @@ def run_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w["name"] if args.bh <= 0 else f"{w['name']} reduced to {BH} (batch, head) slices", "parallelism": f"batch*head sharded over {world} GPU(s), no collective",
-                       "l2": "256 MB buffer written between timed steps", "heads_per_gpu": bh_local,
+                       "l2": "256 MB buffer written between timed steps", "heads_on_rank0": bh_local,
                        "flop_model": "2*D*12*visible_pairs*B*H"},
             "pct_of_bf16_peak": 100.0 * value / (peaks["bf16_tflops"] * world),
             "pct_of_bf16_peak_sustained": (100.0 * value / (peaks["bf16_tflops_sustained"] * world)
                                            if peaks["bf16_tflops_sustained"] else None),
             "peaks": peaks, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
-                    "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world,
+                    "h2d_bytes_per_step": int(h2d) // bh_local * BH, "d2h_bytes_per_step": int(d2h) // bh_local * BH,
                     "pipeline": f"{n_chunks} chunks of (batch, head) slices on upload / compute / download streams"},
             "gpu_launches": int(launches_per_step) * args.steps,
             "device_status": status,
         }
+        pairs_all = visible_pairs_causal(N) * BH
+        for key, gemms, t_ms in (("fwd", 2, fwd_ms), ("bwd", 5, bwd_ms)):
+            tf = 2.0 * D * gemms * pairs_all / (t_ms * 1e-3) / 1e12
+            line[key] = {"ms": t_ms, "tflops": tf, "gemms": gemms, "pct_of_bf16_peak": 100.0 * tf / (peaks["bf16_tflops"] * world)}
+        if sustained is not None:
+            sv = flops_step / (sustained["ms_per_step"] * 1e-3) / 1e12
+            mhz = sustained["clocks"].get("sm_mhz")
+            sustained.update(value=sv, pct_of_bf16_peak=100.0 * sv / (peaks["bf16_tflops"] * world),
+                             pct_of_bf16_peak_sustained=(100.0 * sv / (peaks["bf16_tflops_sustained"] * world)
+                                                         if peaks["bf16_tflops_sustained"] else None),
+                             ms_times_mhz=(sustained["ms_per_step"] * mhz if mhz else None))
+            line["sustained"] = sustained
+        if ttt is not None:
+            line["ttt"] = ttt
         if phase_ms and world == 1:
             # One pass of the path = three launches (scalars + g_dO, g_Q, g_K + g_V).  `achieved` counts
             # the 12 ALGORITHMIC contractions of the pass over the summed device time of the three
@@ -381,6 +445,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks of slices the host-buffer leg is pipelined over")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the >= 2 s loop under the power cap")
+    ap.add_argument("--no-ttt", action="store_true", help="skip the TTT meta-step of bench_ttt.py")
     ap.add_argument("--bh", type=int, default=0,
                     help="profiling only: number of (batch, head) slices instead of the workload's 64")
     args = ap.parse_args()

@@ -114,7 +114,46 @@ def math_attention_fn(N):
     return f
 
 
-def run(args):
+class AttentionTimer:
+    """CUDA events around every call of the attention plugin (forward, backward, double backward),
+    so that a step's device time can be split into attention and everything else."""
+
+    NAMES = ("v7_forward", "v7_backward", "v7_double_backward")
+
+    def __init__(self, module):
+        import torch
+        self.torch, self.module = torch, module
+        self.orig = {n: getattr(module, n) for n in self.NAMES}
+        self.events = {n: [] for n in self.NAMES}
+        self.enabled = False
+        for n in self.NAMES:
+            setattr(module, n, self._wrap(n))
+
+    def _wrap(self, name):
+        fn = self.orig[name]
+
+        def timed(*a, **k):
+            if not self.enabled:
+                return fn(*a, **k)
+            e0, e1 = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **k)
+            e1.record()
+            self.events[name].append((e0, e1))
+            return r
+        return timed
+
+    def restore(self):
+        for n in self.NAMES:
+            setattr(self.module, n, self.orig[n])
+
+    def totals_ms(self):
+        return {n: sum(a.elapsed_time(b) for a, b in ev) for n, ev in self.events.items()}
+
+
+def measure(args, init_process_group=True):
+    """Runs the workload and returns the JSON line as a dict (None on ranks other than 0).  With
+    `init_process_group` false the caller has already set the device and the NCCL group up."""
     import torch
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -126,7 +165,7 @@ def run(args):
     if reference:
         # CPU arm: the reference's math attention; a reduced sample of the workload, stated below
         if rank != 0:
-            return
+            return None
         dev = torch.device("cpu")
         torch.set_num_threads(os.cpu_count() or 1)
         if not args.small:
@@ -140,11 +179,13 @@ def run(args):
             raise SystemExit("bench_ttt.py needs a CUDA device (there is no CPU fallback)")
         torch.cuda.set_device(local)
         dev = torch.device("cuda", local)
-        if world > 1:
+        if world > 1 and init_process_group:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             dist.init_process_group("nccl", device_id=dev)
         sys.path.insert(0, os.path.join(ROOT, "610sample_b200"))
+        import attention_cuda
         from attention import flash_attention_v7
+        timer = AttentionTimer(attention_cuda)
         dtype = torch.bfloat16
         N = cfg["seq"]
         attention = lambda q, k, v: flash_attention_v7(q, k, v, N, 0)
@@ -171,6 +212,7 @@ def run(args):
             dist.barrier()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        timer.enabled = True
         a.record()
         for _ in range(args.steps):
             loss = step()
@@ -178,6 +220,9 @@ def run(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+        timer.enabled = False
+        attn_ms = {n: v / args.steps for n, v in timer.totals_ms().items()}
+        timer.restore()
         tm = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(tm, op=dist.ReduceOp.MAX)
@@ -189,7 +234,9 @@ def run(args):
             loss = step()
         ms = (time.perf_counter() - t0) * 1e3 / args.steps
         peak_mb = None
+        attn_ms = None
     tokens = cfg["batch"] * cfg["seq"] * world
+    line = None
     if rank == 0:
         line = {
             "metric": "ttt_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
@@ -201,12 +248,22 @@ def run(args):
                        "inner_lr": INNER_LR, "sample": sample},
             "outer_loss": float(loss.detach()), "peak_memory_mb": peak_mb,
         }
+        if attn_ms is not None:
+            # device time of the attention plugin calls of rank 0, per step (12 layers x two passes)
+            line["attention_ms_per_step"] = attn_ms
+            line["attention_share"] = sum(attn_ms.values()) / ms
         if reference:
             line["cpu_baseline"] = {"value": line["value"], "unit": "tokens/s", "cores": torch.get_num_threads(),
                                     "kind": "port", "sample": sample or "small configuration, whole"}
-        print(json.dumps(line), flush=True)
-    if world > 1 and not reference:
+    if world > 1 and not reference and init_process_group:
         dist.destroy_process_group()
+    return line
+
+
+def run(args):
+    line = measure(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
 
 
 def main():

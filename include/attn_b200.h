@@ -149,6 +149,18 @@ int attn_b200_last_launch_count(void);
  * code here and returns. */
 int attn_b200_device_status(uint32_t* code);
 
+/* Enqueues on `stream` a 4-byte copy of the current device's status word into
+ * *host_word and returns at once; nothing is synchronised and the device word is
+ * left as it is.  With host_word in page-locked memory the copy is asynchronous, and
+ * a caller that issues it after each call learns of a kernel time-out at the START
+ * of its next call (by then the stream has normally passed the copy) for the price
+ * of reading one host word; on a non-zero value it calls attn_b200_device_status,
+ * which synchronises, clears the word and returns ATTN_EDEVICE.  The module
+ * `attention_cuda` does exactly this, so a time-out surfaces as a Python exception
+ * from the following call.  Has no counterpart in the reference (whose kernels have
+ * no bounded waits). */
+int attn_b200_status_poll_async(uint32_t* host_word, void* stream);
+
 /* Message for the last error of the calling thread ("" if none). */
 const char* attn_b200_last_error(void);
 
@@ -159,7 +171,11 @@ const char* attn_b200_version(void);
  * row-major) = A[128, K] * Bop, with f16/bf16 operands in 128-byte-swizzled
  * shared memory and one tcgen05.mma chain.  flags bit 0: B is given as [K, N]
  * (N contiguous, read as an MN-major operand) instead of [N, K]; bit 1: A is
- * staged by the threads with the software swizzle instead of by TMA.
+ * staged by the threads with the software swizzle instead of by TMA; bit 2: A is
+ * copied to tensor memory and read from there; bit 3: nothing is computed -- one
+ * thread waits, with a limit of about a millisecond, on a barrier that nothing
+ * signals, so that the time-out path runs (status word 0x7003, abort flag, common
+ * teardown that frees tensor memory) without any fault.
  * N in {64, 128}, K in {64, 128}.  Has no counterpart in the reference. */
 int attn_b200_selftest_gemm(const void* A, const void* B, float* C, int32_t N, int32_t K,
                             int32_t dtype, int32_t flags, void* stream);

@@ -122,7 +122,8 @@ def closed_form_all(Q, K, V, dO, g_dQ, g_dK, g_dV, *, window_size: int, chunk_id
                     mask_mode: int = MASK_REFERENCE,
                     compute_dtype: torch.dtype = torch.float64,
                     row_block: int = 512,
-                    heads: Optional[Sequence[int]] = None) -> Dict[str, torch.Tensor]:
+                    heads: Optional[Sequence[int]] = None,
+                    device="cpu") -> Dict[str, torch.Tensor]:
     """Same nine outputs from the closed-form expressions, one (batch, head) and
     one block of query rows at a time.
 
@@ -141,20 +142,22 @@ def closed_form_all(Q, K, V, dO, g_dQ, g_dK, g_dV, *, window_size: int, chunk_id
 
     (reference ``csrc/flash_double_backward_v7.cu:1257-1454, 1583-1675``).
     ``heads`` optionally restricts the flattened (batch*head) indices computed;
-    the others are left zero.
+    the others are left zero.  ``device`` is where the arithmetic runs (the same
+    PyTorch expressions; a GPU only makes N = 16384 in fp64 finish in seconds);
+    the results come back on the CPU.
     """
     B, H, N_q, D = Q.shape
     N_kv = K.shape[2]
     s = 1.0 / math.sqrt(D)
     cd = compute_dtype
-    f = lambda t, n: t.detach().reshape(B * H, n, D)
+    f = lambda t, n: t.detach().reshape(B * H, n, D).to(device)
     Qf, dOf, gQf = f(Q, N_q), f(dO, N_q), f(g_dQ, N_q)
     Kf, Vf, gKf, gVf = f(K, N_kv), f(V, N_kv), f(g_dK, N_kv), f(g_dV, N_kv)
-    z = lambda n: torch.zeros(B * H, n, D, dtype=cd)
+    z = lambda n: torch.zeros(B * H, n, D, dtype=cd, device=device)
     O, dQ, g_dO, g_Q = z(N_q), z(N_q), z(N_q), z(N_q)
     dK, dV, g_K, g_V = z(N_kv), z(N_kv), z(N_kv), z(N_kv)
-    L = torch.zeros(B * H, N_q, dtype=cd)
-    mask_full = visibility_mask(chunk_id, N_q, N_kv, window_size, mask_mode)
+    L = torch.zeros(B * H, N_q, dtype=cd, device=device)
+    mask_full = visibility_mask(chunk_id, N_q, N_kv, window_size, mask_mode, device=device)
     todo = range(B * H) if heads is None else heads
     for bh in todo:
         k, v, gk, gv = (t[bh].to(cd) for t in (Kf, Vf, gKf, gVf))
@@ -187,8 +190,8 @@ def closed_form_all(Q, K, V, dO, g_dQ, g_dK, g_dV, *, window_size: int, chunk_id
             g_dO[bh, r0:r1] = P @ gv + g_dp @ v
             g_K[bh] += s * (dS.T @ gq + g_S.T @ q)
             g_V[bh] += g_dp.T @ do
-    r = lambda t, n: t.reshape(B, H, n, D)
-    return dict(O=r(O, N_q), L=L.reshape(B, H, N_q), dQ=r(dQ, N_q), dK=r(dK, N_kv),
+    r = lambda t, n: t.reshape(B, H, n, D).cpu()
+    return dict(O=r(O, N_q), L=L.reshape(B, H, N_q).cpu(), dQ=r(dQ, N_q), dK=r(dK, N_kv),
                 dV=r(dV, N_kv), g_dO=r(g_dO, N_q), g_Q=r(g_Q, N_q), g_K=r(g_K, N_kv),
                 g_V=r(g_V, N_kv))
 

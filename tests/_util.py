@@ -1,5 +1,6 @@
 """Shared helpers for the tests: fixture loading and tolerance bookkeeping."""
 import glob
+import json
 import os
 
 import numpy as np
@@ -33,3 +34,12 @@ def load_config1_head():
     norms = {n: float(z["norm_" + n]) for n in OUTPUT_NAMES}
     sums = {n: float(z["sum_" + n]) for n in OUTPUT_NAMES}
     return tuple(int(x) for x in z["head"]), inp, out, norms, sums
+
+
+def record_errors(name, table):
+    """Appends a per-output error table (ours / reference path / magnitude) as one JSON line to
+    the file named by $ATTN_PARITY_REPORT, when that is set; the tests pass or fail without it."""
+    path = os.environ.get("ATTN_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"case": name, "errors": table}) + "\n")

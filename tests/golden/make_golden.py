@@ -74,7 +74,9 @@ CASES = [
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path-to-reference-checkout>")
+    ref_root = sys.argv[1]
     ref = load_reference(ref_root)
     torch.set_num_threads(8)
     for name, B, H, N_q, N_kv, D, ws, cid, seed, rdt in CASES:

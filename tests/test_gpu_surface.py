@@ -185,9 +185,10 @@ def test_empty_inputs(mods):
 
 
 def test_double_backward_under_cuda_graph_capture():
-    """The call is capturable: backward and double backward fork onto the library's helper stream
-    and join back, tensor maps travel as kernel parameters, nothing is allocated by the library.
-    The replayed graph must reproduce the eager results bit for bit."""
+    """The call is capturable: under capture every launch stays on the capturing stream (the
+    library's helper stream is used by eager calls only), tensor maps travel as kernel parameters,
+    nothing is allocated by the library.  The replayed graph must reproduce the eager results bit
+    for bit."""
     tcapi = importlib.import_module("610sample_b200.torch_capi")
     capi = importlib.import_module("610sample_b200.capi")
     inp = orc.make_inputs(1, 4, 512, 512, 128, seed=21, dtype=torch.bfloat16)
