@@ -75,22 +75,21 @@ void check_rc(int rc, const char* what) {
 }
 
 // A kernel that gives up on a bounded wait stores a code in the device's status word and returns;
-// its outputs are then meaningless.  Each call of this module ends by enqueueing a copy of that
-// word into a page-locked host word of the device, and begins by looking at the host word: a
-// time-out of an earlier call is reported, without any synchronisation on the good path, as an
-// exception of the first call that starts after the copy has landed.
-struct StatusMirror {
-  torch::Tensor word;   // one int32 in page-locked host memory
-};
-
+// its outputs are then meaningless.  This module registers one page-locked host word per device
+// as a mirror of that status word (the failing kernel writes its code there too) and looks at it
+// at the start of every call: a time-out of an earlier call is reported as an exception of the
+// first call that starts after it, and the good path costs one read of host memory.
 uint32_t* status_mirror(int device) {
-  static StatusMirror mirrors[64];
+  static torch::Tensor words[64];
   static std::mutex mu;
   TORCH_CHECK(device >= 0 && device < 64, "device index out of range");
   std::lock_guard<std::mutex> lock(mu);
-  if (!mirrors[device].word.defined())
-    mirrors[device].word = torch::zeros({1}, torch::dtype(torch::kInt32).pinned_memory(true));
-  return reinterpret_cast<uint32_t*>(mirrors[device].word.data_ptr<int32_t>());
+  if (!words[device].defined()) {
+    words[device] = torch::zeros({1}, torch::dtype(torch::kInt32).pinned_memory(true));
+    check_rc(attn_b200_set_status_mirror(reinterpret_cast<uint32_t*>(words[device].data_ptr<int32_t>())),
+             "attn_b200_set_status_mirror");
+  }
+  return reinterpret_cast<uint32_t*>(words[device].data_ptr<int32_t>());
 }
 
 void raise_if_earlier_call_timed_out(int device) {
@@ -103,10 +102,6 @@ void raise_if_earlier_call_timed_out(int device) {
   snprintf(hex, sizeof(hex), "0x%x", code);
   TORCH_CHECK(rc == ATTN_OK && code == 0u, "an earlier attention kernel on this device gave up on a bounded wait (status ",
               hex, "); its outputs are invalid");
-}
-
-void poll_status(int device, cudaStream_t stream) {
-  check_rc(attn_b200_status_poll_async(status_mirror(device), stream), "attn_b200_status_poll_async");
 }
 
 }  // namespace
@@ -123,7 +118,6 @@ std::vector<torch::Tensor> v7_forward_cuda(torch::Tensor Q, torch::Tensor K, tor
   check_rc(attn_b200_forward(&s, Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr<float>(),
                              at::cuda::getCurrentCUDAStream().stream()),
            "v7_forward");
-  poll_status(Q.device().index(), at::cuda::getCurrentCUDAStream().stream());
   return {O, L};
 }
 
@@ -148,7 +142,6 @@ std::vector<torch::Tensor> v7_backward_cuda(torch::Tensor dO, torch::Tensor Q, t
                               L.data_ptr<float>(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(),
                               scratch.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
            "v7_backward");
-  poll_status(Q.device().index(), at::cuda::getCurrentCUDAStream().stream());
   return {dQ, dK, dV};
 }
 
@@ -181,7 +174,6 @@ std::vector<torch::Tensor> v7_double_backward_cuda(torch::Tensor g_dQ, torch::Te
                                      g_dO.data_ptr(), g_Q.data_ptr(), g_K.data_ptr(), g_V.data_ptr(),
                                      scratch.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
            "v7_double_backward");
-  poll_status(Q.device().index(), at::cuda::getCurrentCUDAStream().stream());
   return {g_dO, g_Q, g_K, g_V};
 }
 

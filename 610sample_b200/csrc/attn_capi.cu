@@ -2,6 +2,7 @@
 // kernel-family dispatch, per-thread error text and the device status word.
 #include "attn_b200.h"
 #include "attn_launch.h"
+#include "tc_primitives.cuh"
 
 #include <cmath>
 #include <cstdarg>
@@ -23,8 +24,9 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-// One status word per device, in device global memory owned by this library.
-__device__ unsigned int g_status_word = 0u;
+// One status block per device, in device global memory owned by this library; the status word
+// is its first member.
+__device__ attn::tc::StatusBlock g_status_block = {0u, 0u, nullptr};
 
 constexpr int kMaxDevices = 64;
 unsigned int* g_status_ptr[kMaxDevices] = {nullptr};
@@ -38,7 +40,7 @@ int status_pointer(unsigned int** out) {
   std::lock_guard<std::mutex> lock(g_status_mutex);
   if (g_status_ptr[dev] == nullptr) {
     void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_status_word);
+    e = cudaGetSymbolAddress(&p, g_status_block);
     if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
     g_status_ptr[dev] = static_cast<unsigned int*>(p);
   }
@@ -274,61 +276,34 @@ int attn_b200_double_backward_static(const attn_shape_t* shape, const void* g_dQ
   REQUIRE_PTR(g_dO); REQUIRE_PTR(g_Q); REQUIRE_PTR(g_K); REQUIRE_PTR(g_V);
   if (L == nullptr && !shape_is_empty(shape)) return fail(ATTN_EINVAL, "L is null");
   const long long rows = (long long)shape->B * shape->H * shape->N_q;
-  if (rows > (long long)ATTN_B200_STATIC_SCRATCH_ROWS)
+  // an empty problem launches nothing and needs no scratch, whatever its nominal row count
+  if (!shape_is_empty(shape) && rows > (long long)ATTN_B200_STATIC_SCRATCH_ROWS)
     return fail(ATTN_ETOOLARGE,
                 "B*H*N_q = %lld query rows exceed the built-in scratch of %d rows; use "
                 "attn_b200_double_backward with caller-provided scratch",
                 rows, (int)ATTN_B200_STATIC_SCRATCH_ROWS);
-  tl_launches = 0;
-  const attn::Geometry g = make_geometry(shape);
-  if (g.BH == 0 || (g.N_q == 0 && g.N_kv == 0)) return ATTN_OK;
-  if (g.N_q == 0 || g.N_kv == 0) {
-    attn::Tensors te;
-    memset(&te, 0, sizeof(te));
-    te.out_g_dO = g_dO; te.out_g_Q = g_Q; te.out_g_K = g_K; te.out_g_V = g_V;
-    return run_empty(attn::OP_DOUBLE_BACKWARD, shape, te, static_cast<cudaStream_t>(stream));
-  }
-
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-  if (dev < 0 || dev >= kMaxDevices) return fail(ATTN_EINVAL, "device index %d out of range", dev);
-  // Makes the device's primary context current on this host thread (tensor-map encoding
-  // is a driver call) without touching the allocator.
-  e = cudaSetDevice(dev);
-  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
-  float* scratch = nullptr;
-  rc = static_scratch_pointer(dev, &scratch);
-  if (rc != ATTN_OK) return rc;
-
   attn::Tensors t;
   memset(&t, 0, sizeof(t));
   t.g_dQ = g_dQ; t.g_dK = g_dK; t.g_dV = g_dV;
   t.dO = dO; t.Q = Q; t.K = K; t.V = V; t.O = O; t.L = L;
   t.out_g_dO = g_dO; t.out_g_Q = g_Q; t.out_g_K = g_K; t.out_g_V = g_V;
-  // Nothing in the scratch has to start at zero: the first kernel writes all three
-  // scalars of every row in range before the later kernels read them.
-  t.Dv = scratch;
-  t.dot2 = scratch + (size_t)rows;
-  t.dot3 = scratch + 2 * (size_t)rows;
-  rc = status_pointer(&t.status);
-  if (rc != ATTN_OK) return rc;
-
-  const bool use_tc = shape->impl == ATTN_IMPL_TENSOR ||
-                      (shape->impl == ATTN_IMPL_AUTO && attn::tc_supported(shape->dtype, shape->D));
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (use_tc) {
-    const char* why = nullptr;
-    e = attn::launch_tc(attn::OP_DOUBLE_BACKWARD, shape->dtype, g, t, cs, &tl_launches, &why,
-                        attn::HVP_PHASE_ALL | attn::HVP_PHASE_SERIAL);   // no helper stream: this entry creates nothing
-    if (e != cudaSuccess)
-      return fail(ATTN_ECUDA, "tensor-core launch failed: %s%s%s", cudaGetErrorString(e), why ? ": " : "", why ? why : "");
-  } else {
-    e = attn::launch_simt(attn::OP_DOUBLE_BACKWARD, shape->dtype, g, t, cs, &tl_launches, attn::HVP_PHASE_ALL);
-    if (e != cudaSuccess) return fail(ATTN_ECUDA, "SIMT launch failed: %s", cudaGetErrorString(e));
+  if (!shape_is_empty(shape)) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(ATTN_EINVAL, "device index %d out of range", dev);
+    float* scratch = nullptr;
+    rc = static_scratch_pointer(dev, &scratch);
+    if (rc != ATTN_OK) return rc;
+    // Nothing in the scratch has to start at zero: the first kernel writes all three
+    // scalars of every row in range before the later kernels read them.
+    t.Dv = scratch;
+    t.dot2 = scratch + (size_t)rows;
+    t.dot3 = scratch + 2 * (size_t)rows;
   }
-  tl_error[0] = 0;
-  return ATTN_OK;
+  // the common tail of every entry point (context binding, empty problems, kernel-family
+  // dispatch); SERIAL keeps every launch on the caller's stream, so no helper stream is created
+  return run(attn::OP_DOUBLE_BACKWARD, shape, t, stream, attn::HVP_PHASE_ALL | attn::HVP_PHASE_SERIAL);
 }
 
 int attn_b200_last_launch_count(void) { return tl_launches; }
@@ -351,13 +326,20 @@ int attn_b200_device_status(uint32_t* code) {
   return ATTN_OK;
 }
 
-int attn_b200_status_poll_async(uint32_t* host_word, void* stream) {
-  if (host_word == nullptr) return fail(ATTN_EINVAL, "host_word is null");
+int attn_b200_set_status_mirror(uint32_t* host_word) {
   unsigned int* p = nullptr;
   int rc = status_pointer(&p);
   if (rc != ATTN_OK) return rc;
-  cudaError_t e = cudaMemcpyAsync(host_word, p, sizeof(uint32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaMemcpyAsync(status word): %s", cudaGetErrorString(e));
+  unsigned int* dev_view = nullptr;
+  if (host_word != nullptr) {
+    void* d = nullptr;
+    cudaError_t e = cudaHostGetDevicePointer(&d, host_word, 0);
+    if (e != cudaSuccess) return fail(ATTN_EINVAL, "host_word is not page-locked, mapped host memory: %s", cudaGetErrorString(e));
+    dev_view = static_cast<unsigned int*>(d);
+  }
+  attn::tc::StatusBlock* blk = reinterpret_cast<attn::tc::StatusBlock*>(p);
+  cudaError_t e = cudaMemcpy(&blk->host_mirror, &dev_view, sizeof(dev_view), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return fail(ATTN_ECUDA, "cudaMemcpy(status mirror): %s", cudaGetErrorString(e));
   return ATTN_OK;
 }
 

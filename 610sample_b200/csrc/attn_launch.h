@@ -17,7 +17,8 @@ enum HvpPhase { HVP_PHASE_PRE = 1, HVP_PHASE_ROW = 2, HVP_PHASE_COL = 4, HVP_PHA
 cudaError_t launch_simt(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,
                         int* launches, int phases);
 
-// tcgen05 tensor-core kernels: f16/bf16, D in {64, 128}.
+// tcgen05 tensor-core kernels: f16/bf16, D a multiple of 16 up to 128 (tiles of width 64 or 128,
+// zero-padded).
 bool tc_supported(int dtype, int D);
 cudaError_t launch_tc(int op, int dtype, const Geometry& g, const Tensors& t, cudaStream_t s,
                       int* launches, const char** err, int phases);

@@ -1,6 +1,6 @@
 // Host side of the tensor-core (tcgen05 / TMEM / TMA) attention kernels on sm_100a:
 // tensor-map encoding, dispatch of the forward / backward / double-backward launches to the
-// kernel files (attn_tc_fb.cu, attn_tc_hvp_row.cu, attn_tc_hvp_col.cu), the row-dot helper of
+// kernel files (attn_tc_fwd.cu, attn_tc_fb.cu, attn_tc_hvp_row.cu, attn_tc_hvp_col.cu), the row-dot helper of
 // the first backward and the tcgen05 primitive self-test.
 #include "attn_common.cuh"
 #include "attn_launch.h"
@@ -240,6 +240,7 @@ cudaError_t launch_hvp_row(int mode, int D, int is_bf16, const TmaMaps& maps, co
 
 cudaError_t launch_fwd_bwd(int kind, int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
                            cudaStream_t s);
+cudaError_t launch_fwd(int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t, cudaStream_t s);
 
 // Kernels of one operation that do not depend on one another (g_Q and g_K/g_V of the double
 // backward; dQ and dK/dV of the backward) run side by side: the second is launched on a helper
@@ -315,11 +316,8 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
   const int D = g.D, bf = Pack<T>::kIsBf16;
   *n = 0;
   if (op == OP_FORWARD) {
-    e = launch_fwd_bwd(0, D, bf, maps, g, t, s);                     // L
-    Tensors t2 = t;
-    t2.L = t.out_L;
-    if (e == cudaSuccess) e = launch_fwd_bwd(1, D, bf, maps, g, t2, s);   // O = P V with P = exp(S - L)
-    *n = 2;
+    e = launch_fwd(D, bf, maps, g, t, s);                              // O and L in one pass (online softmax)
+    *n = 1;
   } else if (op == OP_BACKWARD) {
     const long long rows = (long long)g.BH * g.N_q;
     if (rows > 0) {

@@ -1,34 +1,33 @@
-// Forward and first-backward attention kernels on sm_100a (f16/bf16, D a multiple of 16 up to 128).
+// First-backward attention kernels on sm_100a (f16/bf16, D a multiple of 16 up to 128).
 //
-// Four kinds of one kernel.  A CTA owns 128 STATIONARY rows of one (batch, head) and streams
+// Two kinds of one kernel.  A CTA owns 128 STATIONARY rows of one (batch, head) and streams
 // 64-row tiles of the other axis through as many TMA stages as fit in shared memory (five to eight):
 //
 //   kind      stationary     streamed   tensor-memory score regions        produces
-//   FWD_LSE   Q              K          RA = S                 (x2)        L = log-sum-exp
-//   FWD_OUT   Q              K, V       RA = S                 (x2)        O = P V
 //   BWD_ROW   Q, dO          K, V       RA = S, RB = dP        (x2 each)   dQ = s dS K
 //   BWD_COL   K, V           Q, dO      RA = S^T, RB = dP^T    (x1 each)   dV = P^T dO, dK = s dS^T Q
 //
 // The stationary operands are copied once from shared memory into TENSOR MEMORY and serve from
 // there as the A operand of every score product (a stationary operand left in shared memory
-// would be re-read by each MMA instruction: measured 48 instead of 32 clocks for N = 64).  The math warps read a score region with tcgen05.ld, and write the half-precision
-// operands of the output products (P, dS) back over the score columns they have read; the output
-// products take them from there as their A operand.  The two-pass forward (L first, then
-// P = exp(S - L)) needs no running-maximum rescaling of O; every kind evaluates P the same way.
+// would be re-read by each MMA instruction: measured 48 instead of 32 clocks for N = 64).  The
+// math warps read a score region with tcgen05.ld, evaluate P = exp(S - L) from the saved
+// log-sum-exp, and write the half-precision operands of the output products (P, dS) back over the
+// score columns they have read; the output products take them from there as their A operand.
 // BWD_COL computes transposed scores (keys on the TMEM lanes) so that operand roles are the same
-// as in the row kinds; its per-query scalars (L, Dv) are staged in shared memory per tile.
+// as in the row kind; its per-query scalars (L, Dv) are staged in shared memory per tile.
 // One warp issues every MMA, each batch by one elected lane inside a single branch; with two
-// buffers per region the score products run two tiles ahead.  Head dimensions below the tile
-// width run zero-padded (TMA fills the padding) with the padding k-steps and columns skipped.
-// Result tiles leave through shared memory and TMA stores.
-// Reference kernels: csrc/flash_double_backward_v7.cu:307-552 (forward), :649-1016 (backward).
+// buffers per region the score products of the row kind run two tiles ahead.  Head dimensions
+// below the tile width run zero-padded (TMA fills the padding) with the padding k-steps and
+// columns skipped.  Result tiles leave through shared memory and TMA stores.
+// (The forward pass is in attn_tc_fwd.cu.)
+// Reference kernels: csrc/flash_double_backward_v7.cu:649-1016.
 #include "attn_launch.h"
 #include "tc_common.cuh"
 
 namespace attn {
 namespace tc {
 
-enum FbKind { FB_FWD_LSE = 0, FB_FWD_OUT, FB_BWD_ROW, FB_BWD_COL };
+enum FbKind { FB_BWD_ROW = 2, FB_BWD_COL = 3 };   // numbering of launch_fwd_bwd
 
 constexpr int kFbMmaWarp = 9;
 constexpr int kFbThreads = 320;
@@ -52,12 +51,11 @@ struct FbControl {
 template <int KIND, int D>
 struct FbCfg {
   static constexpr bool kCol = (KIND == FB_BWD_COL);
-  static constexpr bool kBwd = (KIND == FB_BWD_ROW || KIND == FB_BWD_COL);
   static constexpr int kAtoms = D / 64;
-  static constexpr int kNStat = kBwd ? 2 : 1;
-  static constexpr int kNStream = (KIND == FB_FWD_LSE) ? 1 : 2;
+  static constexpr int kNStat = 2;
+  static constexpr int kNStream = 2;
   static constexpr int kBufs = kCol ? 1 : 2;
-  static constexpr int kNOut = (KIND == FB_FWD_LSE) ? 0 : kCol ? 2 : 1;
+  static constexpr int kNOut = kCol ? 2 : 1;
   static constexpr uint32_t kStagingBytes = kNStat * kAtoms * kAtomBytesStat;
   static constexpr uint32_t kStageBytes = kNStream * kAtoms * kAtomBytesStrm;
   static constexpr uint32_t kAuxBytes = 512 + 2048;   // control; per-query scalars / L exchange
@@ -251,13 +249,10 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         const uint64_t dm = smem_desc_sw128(stage_of(j), kAtomBytesStrm, 1024);
         const bool first = (j == 0);
         if (elect_one()) {
-          if constexpr (KIND == FB_FWD_OUT) {          // O += P V
-            _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
-              mma_ts(out0, op_tmem(CF::kRA + 64 * b, ks), dm + moff(1, ks), idesc_out, !(first && ks == 0));
-          } else if constexpr (KIND == FB_BWD_ROW) {   // dQ += dS K
+          if constexpr (KIND == FB_BWD_ROW) {          // dQ += dS K
             _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
               mma_ts(out0, op_tmem(CF::kRB + 64 * b, ks), dm + moff(0, ks), idesc_out, !(first && ks == 0));
-          } else if constexpr (KIND == FB_BWD_COL) {   // dV += P^T dO ; dK += dS^T Q
+          } else {                                     // dV += P^T dO ; dK += dS^T Q
             _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
               mma_ts(out0, op_tmem(CF::kRB, ks), dm + moff(1, ks), idesc_out, !(first && ks == 0));
             _Pragma("unroll") for (int ks = 0; ks < KO; ++ks)
@@ -273,7 +268,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         if (!ok) break;
         tc_fence_after_sync();
         issue_ra(i);
-        if constexpr (CF::kBwd) issue_rb(i);
+        issue_rb(i);
       }
       for (int j = 0; j < n_iter && ok; ++j) {
         const int b = j % kBufs;
@@ -292,7 +287,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        if constexpr (CF::kNOut > 0) issue_out(j);
+        issue_out(j);
         commit(bar_stream_empty(j % CF::kStages));    // every product reading this stage has been issued
         const int nj = j + kBufs;
         if (nj < n_iter) {
@@ -303,11 +298,11 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
             if (!ok) break;
             tc_fence_after_sync();
             issue_ra(nj);                           // buffer b: read by tile j, its outputs issued above
-            if constexpr (CF::kBwd) issue_rb(nj);
+            issue_rb(nj);
           }
         }
       }
-      if constexpr (CF::kNOut > 0) { if (ok) commit(bar_acc_done); }
+      if (ok) commit(bar_acc_done);
     }
   }
   // =========================================================================
@@ -362,16 +357,15 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
 
     // per-row scalars (row kinds), negated so that every use is a packed add / fma
     float2 nL2 = make_float2(-INFINITY, -INFINITY), nDv = make_float2(0.f, 0.f);
-    if constexpr (KIND == FB_FWD_OUT || KIND == FB_BWD_ROW) {
+    if constexpr (KIND == FB_BWD_ROW) {
       if (gidx < g.N_q) {
-        const float L2 = t.L[row_off + gidx] * kLog2e;
+        const float L2 = t.L[row_off + gidx] * kLog2e, Dv = t.Dv[row_off + gidx];
         nL2 = make_float2(-L2, -L2);
-        if constexpr (KIND == FB_BWD_ROW) { const float Dv = t.Dv[row_off + gidx]; nDv = make_float2(-Dv, -Dv); }
+        nDv = make_float2(-Dv, -Dv);
       }
     }
     const float2 sl2 = make_float2(g.scale_log2e, g.scale_log2e);
-    float acc_m = -INFINITY, acc_l = 0.f;        // FWD_LSE: running maximum and sum (log2 domain)
-    float2 p_[16];                               // backward kinds: carried from S to dP
+    float2 p_[16];                               // carried from S to dP
 
     // BWD_COL: per-query scalars of a streamed tile, fetched one tile ahead by the first four warps
     // (thread -> (which, query)) and handed over in shared memory; every warp arrives on the barrier.
@@ -426,23 +420,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_ra_free);
       }
-      if constexpr (KIND == FB_FWD_LSE) {
-        float x[32], mx = -INFINITY;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const bool vis = !masked || ((uint32_t)(first + e - vlo) < vspan);
-          x[e] = vis ? __uint_as_float(s_[e >> 4][e & 15]) * g.scale_log2e : -INFINITY;
-          mx = fmaxf(mx, x[e]);
-        }
-        if (mx > -INFINITY) {
-          const float mn = fmaxf(acc_m, mx);
-          float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) { sum0 += ex2(x[e] - mn); sum1 += ex2(x[e + 1] - mn); }
-          acc_l = acc_l * ex2(acc_m - mn) + (sum0 + sum1);
-          acc_m = mn;
-        }
-      } else {
+      {
         uint32_t kp[2][8];
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
@@ -460,12 +438,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
             p_[ch * 8 + (e >> 1)] = pp;
             kp[ch][e >> 1] = Pack<T>::pack(pp.x, pp.y);
           }
-        if constexpr (KIND == FB_FWD_OUT) {
-          // P over the S columns this thread has read
-          tmem_st8(ra, kp[0]);
-          tmem_st8(ra + 8, kp[1]);
-          tmem_st_wait();
-        } else {
+        {
           // ---------------- dP -> dS (and P^T for the column kind) ------------------
           ok = mbar_wait(bar_rb_full(b), (it / kBufs) & 1, abort_flag, t.status, wait_code(KCODE, 8));
           ok = __all_sync(0xffffffffu, ok);
@@ -510,22 +483,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
     }
 
     // ---------------- results ------------------------------------------------------
-    if constexpr (KIND == FB_FWD_LSE) {
-      float* xm = aux_f;            // [128]
-      float* xl = aux_f + 128;      // [128]
-      if (half == 1) { xm[row] = acc_m; xl[row] = acc_l; }
-      named_barrier_sync(1, kMathThreads);
-      if (half == 0 && gidx < g.N_q) {
-        const float m1 = xm[row], l1 = xl[row];
-        const float mt = fmaxf(acc_m, m1);
-        float L = -INFINITY;
-        if (mt > -INFINITY) {
-          const float lt = acc_l * ex2(acc_m - mt) + l1 * ex2(m1 - mt);
-          L = (mt + log2f(lt)) * kLn2;
-        }
-        t.out_L[row_off + gidx] = L;
-      }
-    } else {
+    {
       if (n_iter > 0 && ok) ok = mbar_wait(bar_acc_done, 0, abort_flag, t.status, wait_code(KCODE, 10));
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
@@ -537,7 +495,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
       for (int o = 0; o < CF::kNOut; ++o) {
         float mul = 1.f;
         if constexpr (KIND == FB_BWD_ROW) mul = g.scale;
-        else if constexpr (KIND == FB_BWD_COL) mul = (o == 0) ? 1.f : g.scale;
+        else mul = (o == 0) ? 1.f : g.scale;
         const uint32_t tile = staging + (uint32_t)o * kAtoms * kAtomBytesStat;
         uint32_t v[kChunks][16];
 #pragma unroll
@@ -568,7 +526,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
       named_barrier_sync(2, kMathWarps * 32);
       if (threadIdx.x == 0) {
         for (int o = 0; o < CF::kNOut; ++o) {
-          const int id = (KIND == FB_FWD_OUT) ? TO_O : (KIND == FB_BWD_ROW) ? TO_dQ : (o == 0 ? TO_dV : TO_dK);
+          const int id = (KIND == FB_BWD_ROW) ? TO_dQ : (o == 0 ? TO_dV : TO_dK);
           for (int a = 0; a * 64 < g.D; ++a)
             tma_store_3d(&maps.out[id], staging + (uint32_t)(o * kAtoms + a) * kAtomBytesStat, a * 64, r0, bh);
         }
@@ -607,15 +565,10 @@ static cudaError_t launch_fb(const TmaMaps& maps, const Geometry& g_in, const Te
 
 template <int D, typename T>
 static cudaError_t launch_fb_kind(int kind, const TmaMaps& maps, const Geometry& g, const Tensors& t, cudaStream_t s) {
-  switch (kind) {
-    case FB_FWD_LSE: return launch_fb<FB_FWD_LSE, D, T>(maps, g, t, s);
-    case FB_FWD_OUT: return launch_fb<FB_FWD_OUT, D, T>(maps, g, t, s);
-    case FB_BWD_ROW: return launch_fb<FB_BWD_ROW, D, T>(maps, g, t, s);
-    default: return launch_fb<FB_BWD_COL, D, T>(maps, g, t, s);
-  }
+  return kind == FB_BWD_ROW ? launch_fb<FB_BWD_ROW, D, T>(maps, g, t, s) : launch_fb<FB_BWD_COL, D, T>(maps, g, t, s);
 }
 
-// kind: 0 forward L, 1 forward O, 2 backward dQ, 3 backward dK and dV
+// kind: 2 backward dQ, 3 backward dK and dV
 cudaError_t launch_fwd_bwd(int kind, int D, int is_bf16, const TmaMaps& maps, const Geometry& g, const Tensors& t,
                            cudaStream_t s) {
   if (D <= 64) return is_bf16 ? launch_fb_kind<64, __nv_bfloat16>(kind, maps, g, t, s) : launch_fb_kind<64, __half>(kind, maps, g, t, s);

@@ -50,6 +50,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // roles see the flag in their own waits and leave as well.
 constexpr long long kWaitLimitCycles = 4000000000LL;
 
+// The device status word is the first member of this block (one per device, owned by the
+// library).  `host_mirror`, when set, is a page-locked host word that a kernel giving up on a wait
+// writes its code to as well, so that the host can notice a time-out by reading its own memory,
+// without a copy or a synchronisation.
+struct StatusBlock {
+  unsigned int word;
+  unsigned int reserved;
+  unsigned int* host_mirror;
+};
+
+__device__ __forceinline__ void report_timeout(unsigned int* status, uint32_t code) {
+  if (status == nullptr) return;
+  atomicCAS(status, 0u, code);
+  unsigned int* mirror = *reinterpret_cast<unsigned int* volatile*>(&reinterpret_cast<StatusBlock*>(status)->host_mirror);
+  if (mirror != nullptr) {
+    *reinterpret_cast<volatile unsigned int*>(mirror) = code;
+    __threadfence_system();
+  }
+}
+
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                                 unsigned int* status, uint32_t code, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -59,7 +79,7 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
     if (*abort_flag != 0u) return false;
     if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1u;
-      if (status != nullptr) atomicCAS(status, 0u, code);
+      report_timeout(status, code);
       return false;
     }
   }

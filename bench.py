@@ -20,8 +20,9 @@ Printed JSON line: metric = algorithmic TFLOP/s of the HVP
 in and the four results copied back inside the timed region.
 
 ``--impl reference`` times the reference's CPU path (its PyTorch math attention
-differentiated twice; restated in oracle/attention_oracle.py because the
-reference checkout is not present on the GPU box) on the host cores.
+differentiated twice) on the host cores: the reference's own ``reference_attention``
+when oracle/build_ref.py has byte-compiled it into oracle/_ref/, else the restatement
+in oracle/attention_oracle.py (the reference checkout itself is not on the GPU box).
 """
 from __future__ import annotations
 
@@ -115,21 +116,37 @@ class ClockSampler:
                     samples=len(sm), reasons=sorted(reasons))
 
 
+def cpu_path(orc):
+    """The CPU implementation that is timed: the reference's own `reference_attention` and
+    `make_sw_causal_mask` (e2e/ttt_pytorch/model.py, byte-compiled into oracle/_ref/ by
+    oracle/build_ref.py) when that file is present -- kind "reference" -- and otherwise the
+    restatement of the same five lines in oracle/attention_oracle.py -- kind "port"."""
+    try:
+        import build_ref
+        ref = build_ref.load_python_reference()
+    except Exception:  # noqa: BLE001
+        ref = None
+    if ref is not None:
+        return ref.reference_attention, (lambda N: ref.make_sw_causal_mask(0, N, N, N, "cpu")), "reference"
+    return orc.math_attention, (lambda N: orc.visibility_mask(0, N, N, N)), "port"
+
+
 def cpu_hvp_seconds(orc, torch, n_heads: int, N: int, D: int, seed: int = 0):
     """Time the reference CPU path (math attention, double autograd) on `n_heads`
-    (batch, head) slices of the workload; returns (seconds for the HVP step, threads)."""
+    (batch, head) slices of the workload; returns (seconds for the HVP step, threads, kind)."""
+    attention, make_mask, kind = cpu_path(orc)
     inp = orc.make_inputs(1, n_heads, N, N, D, seed=seed, dtype=torch.float32)
-    mask = orc.visibility_mask(0, N, N, N)
+    mask = make_mask(N)
     total = 0.0
     for h in range(n_heads):
         q, k, v, do = (inp[n][:, h:h + 1].clone().requires_grad_(True) for n in ("Q", "K", "V", "dO"))
-        O = orc.math_attention(q, k, v, mask)
+        O = attention(q, k, v, mask)
         dQ, dK, dV = torch.autograd.grad(O, [q, k, v], grad_outputs=do, create_graph=True)
         hsum = (dQ * inp["g_dQ"][:, h:h + 1]).sum() + (dK * inp["g_dK"][:, h:h + 1]).sum() + (dV * inp["g_dV"][:, h:h + 1]).sum()
         t0 = time.perf_counter()
         torch.autograd.grad(hsum, [do, q, k, v])
         total += time.perf_counter() - t0
-    return total, torch.get_num_threads()
+    return total, torch.get_num_threads(), kind
 
 
 def run_reference(args):
@@ -148,7 +165,7 @@ def run_reference(args):
         cpu_hvp_seconds(orc, torch, 1, w["N"], w["D"])
     times = []
     for s in range(args.steps):
-        sec, threads = cpu_hvp_seconds(orc, torch, heads_per_step, w["N"], w["D"], seed=s)
+        sec, threads, kind = cpu_hvp_seconds(orc, torch, heads_per_step, w["N"], w["D"], seed=s)
         times.append(sec)
     sec = sum(times) / len(times)
     value = flops_head * heads_per_step / sec / 1e12
@@ -158,7 +175,7 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": w["name"], "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -426,9 +443,9 @@ def run_ours(args):
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
             n_cpu = 16
-            sec, threads = cpu_hvp_seconds(orc, torch, n_cpu, N, D)
+            sec, threads, kind = cpu_hvp_seconds(orc, torch, n_cpu, N, D)
             cpu_val = 2.0 * D * HVP_GEMMS * visible_pairs_causal(N) * n_cpu / sec / 1e12
-            line["cpu_baseline"] = {"value": cpu_val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            line["cpu_baseline"] = {"value": cpu_val, "unit": "TFLOP/s", "cores": threads, "kind": kind,
                                     "sample": f"{n_cpu} of {BH} (batch, head) slices, fp32 math attention, "
                                               f"second autograd.grad only ({sec:.2f} s timed)"}
         print(json.dumps(line), flush=True)

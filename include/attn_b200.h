@@ -100,7 +100,9 @@ int attn_b200_double_backward(const attn_shape_t* shape, const void* g_dQ, const
 /* The same computation restricted to some of its kernels, for profiling one
  * kernel at a time: `phases` is a bit mask of 1 (per-row scalars Dv, dot2, dot3
  * into scratch, and g_dO), 2 (g_Q; needs the scalars in scratch) and 4 (g_K and
- * g_V; needs the scalars too).  7 is attn_b200_double_backward.  The reference
+ * g_V; needs the scalars too).  7 is attn_b200_double_backward.  In the fp32 CUDA-core
+ * family the scalars and both row-side outputs come from ONE kernel, so there masks 1
+ * and 2 each run that kernel whole (scalars, g_dO and g_Q are all written).  The reference
  * splits its double backward the same way into kernel A (rows, two passes) and
  * kernel B (columns), csrc/flash_double_backward_v7.cu:1778-1807. */
 int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ, const void* g_dK,
@@ -127,8 +129,13 @@ int attn_b200_double_backward_phases(const attn_shape_t* shape, const void* g_dQ
  * launched; use attn_b200_double_backward with your own scratch for those.
  *
  * The first call on a device looks up the device address of the array (one
- * cudaGetSymbolAddress, cached afterwards).  Make that first call outside any stream
- * capture.  All calls on one device share the one array and it keeps whatever the
+ * cudaGetSymbolAddress, cached afterwards), and the first launch of each kernel variant
+ * (input type x head-dimension class x kernel family) makes the driver load that
+ * kernel's code; both are driver-side work at the call site.  So make one warm-up call
+ * per variant you will use at start-up, outside any stream capture: from the second
+ * call on, nothing is allocated or loaded.  An empty problem (B, H, N_q or N_kv zero)
+ * launches nothing and is accepted whatever its row count.
+ * All calls on one device share the one array and it keeps whatever the
  * last call left there; nothing in it needs clearing, since each call rewrites every
  * value it later reads.  Because of the sharing, two calls whose kernels can overlap
  * on the GPU (different streams, or different host threads) race on the scratch and
@@ -149,17 +156,16 @@ int attn_b200_last_launch_count(void);
  * code here and returns. */
 int attn_b200_device_status(uint32_t* code);
 
-/* Enqueues on `stream` a 4-byte copy of the current device's status word into
- * *host_word and returns at once; nothing is synchronised and the device word is
- * left as it is.  With host_word in page-locked memory the copy is asynchronous, and
- * a caller that issues it after each call learns of a kernel time-out at the START
- * of its next call (by then the stream has normally passed the copy) for the price
- * of reading one host word; on a non-zero value it calls attn_b200_device_status,
- * which synchronises, clears the word and returns ATTN_EDEVICE.  The module
- * `attention_cuda` does exactly this, so a time-out surfaces as a Python exception
- * from the following call.  Has no counterpart in the reference (whose kernels have
- * no bounded waits). */
-int attn_b200_status_poll_async(uint32_t* host_word, void* stream);
+/* Registers a page-locked host word (cudaHostAlloc / cudaHostRegister memory, mapped into
+ * the device's address space) as a mirror of the current device's status word: a kernel
+ * that gives up on a bounded wait writes its code there as well as into the device word.
+ * A caller can then notice a time-out at the start of its next call by reading its own
+ * memory -- no copy, no synchronisation, nothing on the good path -- and fetch and clear
+ * the device word with attn_b200_device_status.  The module `attention_cuda` does exactly
+ * this, so a time-out surfaces as a Python exception of a following call.  NULL
+ * unregisters.  Synchronous (one 8-byte copy); call it at start-up.  Has no counterpart in
+ * the reference (whose kernels have no bounded waits). */
+int attn_b200_set_status_mirror(uint32_t* host_word);
 
 /* Message for the last error of the calling thread ("" if none). */
 const char* attn_b200_last_error(void);

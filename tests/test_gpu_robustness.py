@@ -3,8 +3,8 @@
 * the bounded-wait time-out path runs once, through the primitive self-test (one thread waits
   about a millisecond on a barrier nothing signals): the status word carries the code, the kernel
   returns, and the library works bit-identically afterwards;
-* a time-out reaches a caller of the `attention_cuda` module as an exception of a following call,
-  without a synchronisation on the good path;
+* a time-out reaches a caller of the `attention_cuda` module as an exception of its next call (the
+  kernel writes its code to a page-locked host word the module looks at; nothing on the good path);
 * the tcgen05 primitive self-test (TMA + MMA chain, every operand placement) against torch.matmul;
 * guard bands: every output, L and the scratch are carved out of NaN-filled buffers at ragged
   shapes; after the calls the bands are untouched (plain stores and TMA stores alike);
@@ -67,11 +67,9 @@ def test_timeout_surfaces_as_an_exception_of_a_following_module_call():
         sys.path.insert(0, PKG_DIR)
     import attention_cuda
     q = torch.randn(1, 1, 64, 64, device=DEV, dtype=torch.bfloat16)
-    attention_cuda.v7_forward(q, q, q, 64, 0)    # creates the host mirror of the status word
+    attention_cuda.v7_forward(q, q, q, 64, 0)    # registers the module's host mirror of the status word
     torch.cuda.synchronize()
-    _run_timeout_selftest()
-    attention_cuda.v7_forward(q, q, q, 64, 0)    # good path: no synchronisation; ends by polling the status word
-    torch.cuda.synchronize()
+    _run_timeout_selftest()                      # the kernel that gives up writes its code to the mirror too
     with pytest.raises(RuntimeError, match="bounded wait"):
         attention_cuda.v7_forward(q, q, q, 64, 0)
     O, _ = attention_cuda.v7_forward(q, q, q, 64, 0)     # reported once, cleared

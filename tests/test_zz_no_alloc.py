@@ -60,6 +60,50 @@ def test_static_scratch_fp32_kernels_and_repeat():
         assert torch.equal(a, c) and torch.equal(b, c)
 
 
+def test_static_scratch_at_exactly_its_capacity_and_without_allocating():
+    """The largest accepted problem (B*H*N_q == ATTN_B200_STATIC_SCRATCH_ROWS: every element of
+    the fixed array is used) gives the regular entry point's results bit for bit, and a second
+    call with caller-provided outputs leaves the device's free memory and PyTorch's allocation
+    counter exactly where they were."""
+    B, H, N, D = 16, 16, 4096, 16
+    assert B * H * N == capi.STATIC_SCRATCH_ROWS
+    inp, args = _problem(B, H, N, N, D, N, 0, 24, torch.bfloat16)
+    want = tcapi.double_backward(*args)
+    outs = tuple(torch.full_like(t, float("nan")) for t in want)
+    tcapi.double_backward_static(*args, out=outs)          # first call: kernels and the array's address are loaded
+    torch.cuda.synchronize()
+    for a, b, n in zip(outs, want, ("g_dO", "g_Q", "g_K", "g_V")):
+        assert torch.equal(a, b), n
+    for t in outs:
+        t.fill_(float("nan"))
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    tcapi.double_backward_static(*args, out=outs)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0 and torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == reserved0
+    for a, b, n in zip(outs, want, ("g_dO", "g_Q", "g_K", "g_V")):
+        assert torch.equal(a, b), n
+    assert capi.device_status() == 0
+
+
+def test_static_scratch_empty_problem_beyond_capacity_is_not_refused():
+    """N_kv == 0: nothing to compute, the outputs are zero, and the row limit does not apply."""
+    rows_over = capi.STATIC_SCRATCH_ROWS // 64 + 1
+    q = torch.full((rows_over, 1, 64, 64), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kv = torch.empty(rows_over, 1, 0, 64, device=DEV, dtype=torch.bfloat16)
+    L = torch.zeros(rows_over, 1, 64, device=DEV)
+    s = capi.make_shape(rows_over, 1, 64, 0, 64, 64, 0, 0, capi.ATTN_BF16)
+    g_dO, g_Q = torch.full_like(q, float("nan")), torch.full_like(q, float("nan"))
+    p = q.data_ptr()
+    rc = capi.lib().attn_b200_double_backward_static(s, p, None, None, p, p, None, None, p, L.data_ptr(),
+                                                     g_dO.data_ptr(), g_Q.data_ptr(), None, None, torch.cuda.current_stream().cuda_stream)
+    assert rc == capi.ATTN_OK, capi.lib().attn_b200_last_error()
+    torch.cuda.synchronize()
+    assert float(g_dO.float().abs().max()) == 0.0 and float(g_Q.float().abs().max()) == 0.0
+
+
 def test_static_scratch_rejects_problems_beyond_its_capacity():
     q = torch.zeros(1, 1, 64, 64, device=DEV, dtype=torch.bfloat16)
     L = torch.zeros(1, 1, 64, device=DEV)
