@@ -45,3 +45,22 @@ def test_meta_step_matches_math_attention_path():
     for n in ref[1]:
         scale = max(1.0, float(ref[1][n].abs().max()))
         assert torch.allclose(ours[1][n], ref[1][n], atol=5e-2 * scale, rtol=5e-2), n
+
+
+@pytest.mark.gpu
+def test_attention_only_meta_step_matches_math_attention_path():
+    """The reference's attention-only meta-step (e2e/tests/test_ttt_e2e_pytorch.py:754-818: chunks of
+    a token stream, K/V history left-padded with zeros, gradient of sum(O) with respect to the three
+    projections under create_graph, meta-loss = sum of those gradients, one backward) on its `small`
+    and `med` shapes: the kernel arm against the PyTorch math-attention arm of bench_attn_meta.py."""
+    import bench_attn_meta as bam
+    dev = torch.device("cuda")
+    kern, math_ = bam.kernel_attention(), bam.math_attention()
+    for name in ("small", "med"):
+        shape = bam.SHAPES[name]
+        loss_k, g_k = bam.run_step(torch, kern, 2, shape, dev, torch.bfloat16, seed=3)
+        loss_m, g_m = bam.run_step(torch, math_, 2, shape, dev, torch.bfloat16, seed=3)
+        assert abs(float(loss_k) - float(loss_m)) <= 5e-2 * max(1.0, abs(float(loss_m)))
+        for a, b, n in zip(g_k, g_m, ("W_q", "W_k", "W_v")):
+            scale = max(1e-6, float(b.float().abs().max()))
+            assert float((a.float() - b.float()).abs().max()) <= 5e-2 * scale, (name, n)
