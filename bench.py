@@ -45,10 +45,10 @@ HVP_GEMMS = 12          # algorithmic contractions of the double backward
 ROW_KERNEL_GEMMS = 7    # contractions the g_Q kernel executes (5 score + 2 output)
 PRE_KERNEL_GEMMS = 7    # scalars + g_dO kernel (5 score + 2 output)
 COL_KERNEL_GEMMS = 8
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture at 16 (batch, head)
-# slices (profiles/hvp_kernels_bf16_causal_N4096_D128_16heads_ncu_full.md); traffic grows in
-# proportion to the number of slices, so the bench scales it by BH / 16.
-NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 199.9e6, "row": 172.7e6, "col": 138.0e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel, from an `ncu --set full`
+# capture of this bench at 16 (batch, head) slices; traffic grows in proportion to the number of
+# slices, so the bench scales it by BH / 16.  To be refreshed whenever a kernel changes.
+NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 193.3e6, "row": 173.6e6, "col": 137.3e6}
 
 
 def visible_pairs_causal(n: int) -> int:
@@ -147,6 +147,46 @@ def cpu_hvp_seconds(orc, torch, n_heads: int, N: int, D: int, seed: int = 0):
         torch.autograd.grad(hsum, [do, q, k, v])
         total += time.perf_counter() - t0
     return total, torch.get_num_threads(), kind
+
+
+def reference_kernels_block(torch, tcapi, orc):
+    """Secondary, like-for-like comparison: the reference's own CUDA kernels (compiled unchanged for
+    sm_100a into oracle/_ref/ by oracle/build_ref.py; they exist for D in {64, 80, 96} only, so not
+    for the headline D = 128) and this repository's kernels on the same GPU and inputs: bf16 causal
+    N = 4096, D = 64, 64 (batch, head) slices.  None when the reference build is absent."""
+    try:
+        import build_ref
+        ref = build_ref.load_module()
+    except Exception:  # noqa: BLE001
+        ref = None
+    if ref is None:
+        return None
+    B, H, N, D = 4, 16, 4096, 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda: torch.randn(B, H, N, D, device="cuda", generator=g).to(torch.bfloat16)
+    Q, K, V, dO, gQ, gK, gV = (mk() for _ in range(7))
+
+    def timeit(f, n=5):
+        for _ in range(2):
+            f()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            f()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    out = {"workload": "bf16 causal B4 H16 N4096 D64", "note": "the reference builds D in {64, 80, 96}; no D = 128 kernel exists to compare the headline with"}
+    O, L = tcapi.forward(Q, K, V, N, 0)
+    Or, Lr = ref.v7_forward(Q, K, V, N, 0)
+    for tag, fwd, bwd, hvp, o, l in (("ours", tcapi.forward, tcapi.backward, tcapi.double_backward, O, L),
+                                     ("reference", ref.v7_forward, ref.v7_backward, ref.v7_double_backward, Or, Lr)):
+        out[tag] = {"fwd_ms": timeit(lambda: fwd(Q, K, V, N, 0)), "bwd_ms": timeit(lambda: bwd(dO, Q, K, V, o, l, N, 0)),
+                    "hvp_ms": timeit(lambda: hvp(gQ, gK, gV, dO, Q, K, V, o, l, N, 0))}
+    out["speedup"] = {k: out["reference"][k] / out["ours"][k] for k in ("fwd_ms", "bwd_ms", "hvp_ms")}
+    return out
 
 
 def run_reference(args):
@@ -258,22 +298,25 @@ def run_ours(args):
     ms = sum(a.elapsed_time(b) for a, b in ev)
     ms_per_step = sharding.max_over_ranks(ms, dev) / args.steps
 
-    # ---- per-kernel timing of the dominant kernel (rank 0, single-GPU roofline) --
+    # ---- per-kernel timing (single-GPU roofline): the three kernels of a pass, launched one after
+    # the other as in a step (serially, each between its own pair of events), L2 flushed before
+    # each pass, no host synchronisation inside the loop -- the regime of the timed region above
     phase_ms = {}
     if hasattr(capi.lib(), "attn_b200_double_backward_phases"):
-        for name, mask_bits in (("pre", 1), ("row", 2), ("col", 4)):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            tot = 0.0
-            reps = max(3, min(args.steps, 10))
-            for _ in range(reps):
-                flush.zero_()
+        reps = max(3, min(args.steps, 20))
+        names = (("pre", 1), ("row", 2), ("col", 4))
+        pev = {n: [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)] for n, _ in names}
+        for r in range(reps):
+            flush.zero_()
+            for name, mask_bits in names:
+                a, b = pev[name][r]
                 a.record()
                 tcapi.double_backward_phases(g["g_dQ"], g["g_dK"], g["g_dV"], g["dO"], g["Q"], g["K"], g["V"], O, L,
                                              ws, cid, mm, scratch=scratch, out=outs, phases=mask_bits)
                 b.record()
-                torch.cuda.synchronize()
-                tot += a.elapsed_time(b)
-            phase_ms[name] = tot / reps
+        torch.cuda.synchronize()
+        for name, _ in names:
+            phase_ms[name] = sum(a.elapsed_time(b) for a, b in pev[name]) / reps
 
     # ---- forward and first backward at the same shape (rank-local slices) ----------
     def time_call(fn, reps):
@@ -440,6 +483,10 @@ def run_ours(args):
                                                 "algorithmic bytes of the pass: %.0f" % ((12 * N * D * 2 + 4 * N) * BH),
                                 "peak_source": peaks["source"], "kernel_ms": phase_ms,
                                 "dominant_kernel": "hvp_" + dom, "executed": executed}
+        if world == 1 and not args.no_ref_kernels:
+            rk = reference_kernels_block(torch, tcapi, orc)
+            if rk is not None:
+                line["vs_reference_kernels"] = rk
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
             n_cpu = 16
@@ -464,6 +511,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the >= 2 s loop under the power cap")
     ap.add_argument("--no-ttt", action="store_true", help="skip the TTT meta-step of bench_ttt.py")
+    ap.add_argument("--no-ref-kernels", action="store_true", help="skip the comparison with the reference's own CUDA kernels")
     ap.add_argument("--bh", type=int, default=0,
                     help="profiling only: number of (batch, head) slices instead of the workload's 64")
     args = ap.parse_args()
