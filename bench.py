@@ -320,19 +320,17 @@ def run_ours(args):
 
     # ---- forward and first backward at the same shape (rank-local slices) ----------
     def time_call(fn, reps):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        tot = 0.0
-        for _ in range(reps):
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        for a, b in evs:
             flush.zero_()
             a.record()
             fn()
             b.record()
-            torch.cuda.synchronize()
-            tot += a.elapsed_time(b)
-        return tot / reps
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / reps
 
     bwd_scratch = torch.empty(capi.lib().attn_b200_backward_scratch_bytes(s) // 4 + 4, dtype=torch.float32, device=dev)
-    fb_reps = max(3, min(args.steps, 10))
+    fb_reps = max(3, min(args.steps, 20))
     fwd_fn = lambda: tcapi.forward(g["Q"], g["K"], g["V"], ws, cid, mm)
     bwd_fn = lambda: tcapi.backward(g["dO"], g["Q"], g["K"], g["V"], O, L, ws, cid, mm, scratch=bwd_scratch)
     for _ in range(2):
