@@ -26,7 +26,7 @@ LIB = os.path.join(HERE, "libattn_b200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC]
-CU_SOURCES = ["attn_capi.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc_fb.cu", "attn_tc_fwd.cu", "attn_tc_hvp_row.cu", "attn_tc_hvp_col.cu"]
+CU_SOURCES = ["attn_capi.cu", "attn_prep.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc_fb.cu", "attn_tc_fwd.cu", "attn_tc_hvp_row.cu", "attn_tc_hvp_col.cu"]
 HEADERS = ["attn_common.cuh", "attn_launch.h", "tc_primitives.cuh", "tc_common.cuh", os.path.join(INCLUDE, "attn_b200.h")]
 
 

@@ -24,7 +24,7 @@ EXPORTS = (
     "attn_b200_double_backward_scratch_bytes", "attn_b200_double_backward",
     "attn_b200_double_backward_phases", "attn_b200_double_backward_static",
     "attn_b200_last_launch_count", "attn_b200_device_status", "attn_b200_last_error",
-    "attn_b200_version", "attn_b200_selftest_gemm", "attn_b200_set_status_mirror",
+    "attn_b200_version", "attn_b200_selftest_gemm", "attn_b200_set_status_mirror", "attn_b200_qk_norm_rope",
 )
 
 
@@ -54,6 +54,7 @@ def lib() -> C.CDLL:
         L.attn_b200_double_backward_static.argtypes = [C.POINTER(Shape)] + [vp] * 13 + [vp]
         L.attn_b200_device_status.argtypes = [C.POINTER(C.c_uint32)]
         L.attn_b200_set_status_mirror.argtypes = [vp]
+        L.attn_b200_qk_norm_rope.argtypes = [vp, vp, vp, vp] + [C.c_int32] * 5 + [C.c_float, C.c_int32, vp]
         L.attn_b200_last_error.restype = C.c_char_p
         L.attn_b200_version.restype = C.c_char_p
         L.attn_b200_selftest_gemm.argtypes = [vp, vp, fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp]

@@ -177,7 +177,33 @@ std::vector<torch::Tensor> v7_double_backward_cuda(torch::Tensor g_dQ, torch::Te
   return {g_dO, g_Q, g_K, g_V};
 }
 
+// x [n_tok, H, d] -> [1, H, n_tok, d]: RMS normalisation (rows >= norm_from, when a weight is given),
+// rotary embedding with freqs [positions, d/2, 2] (float32 cos, sin), layout change; one kernel.
+torch::Tensor qk_norm_rope_cuda(torch::Tensor x, c10::optional<torch::Tensor> weight, torch::Tensor freqs, int pos0,
+                                double eps, int norm_from) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 3, "x must be a CUDA tensor [n_tok, H, d]");
+  TORCH_CHECK(freqs.is_cuda() && freqs.scalar_type() == at::kFloat && freqs.dim() == 3 && freqs.size(2) == 2 &&
+              freqs.size(1) * 2 == x.size(2), "freqs must be float32 [positions, d/2, 2]");
+  TORCH_CHECK(pos0 >= 0 && pos0 + x.size(0) <= freqs.size(0), "positions out of the range of freqs");
+  c10::cuda::CUDAGuard guard(x.device());
+  x = x.contiguous();
+  freqs = freqs.contiguous();
+  torch::Tensor w;
+  if (weight.has_value() && weight->defined()) {
+    TORCH_CHECK(weight->is_cuda() && weight->numel() == x.size(2), "weight must be a CUDA tensor [d]");
+    w = weight->to(x.scalar_type()).contiguous();
+  }
+  auto out = torch::empty({1, x.size(1), x.size(0), x.size(2)}, x.options());
+  check_rc(attn_b200_qk_norm_rope(x.data_ptr(), w.defined() ? w.data_ptr() : nullptr, freqs.data_ptr<float>(), out.data_ptr(),
+                                  (int32_t)x.size(0), (int32_t)x.size(1), (int32_t)x.size(2), pos0, norm_from, (float)eps,
+                                  dtype_code(x), at::cuda::getCurrentCUDAStream().stream()),
+           "qk_norm_rope");
+  return out;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("qk_norm_rope", &qk_norm_rope_cuda, "fused RMS norm + rotary embedding + [n_tok,H,d] -> [1,H,n_tok,d]",
+        py::arg("x"), py::arg("weight"), py::arg("freqs"), py::arg("pos0") = 0, py::arg("eps") = 1e-6, py::arg("norm_from") = 0);
   m.def("v7_forward", &v7_forward_cuda, "Rectangular sliding-window flash attention forward -> [O, L]",
         py::arg("Q"), py::arg("K"), py::arg("V"), py::arg("window_size"), py::arg("chunk_id"),
         py::arg("mask_mode") = 0, py::arg("impl") = 0);

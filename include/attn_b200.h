@@ -146,6 +146,21 @@ int attn_b200_double_backward_static(const attn_shape_t* shape, const void* g_dQ
                                      const void* V, const void* O, const float* L, void* g_dO,
                                      void* g_Q, void* g_K, void* g_V, void* stream);
 
+/* The step in front of the attention calls, fused into one pass: per-(token, head) RMS
+ * normalisation with a learned weight, rotary position embedding, and the layout change
+ * from the projections' [n_tok, H, d] to the kernels' [1, H, n_tok, d].  The reference does
+ * these as separate eager operations followed by permute + contiguous
+ * (e2e/ttt_pytorch/model.py:76-84 RMSNorm, :96-116 apply_rotary_emb, :260-263 and
+ * :309-316 their use, :182-184 the permutes).  x: [n_tok, H, d] contiguous; weight: [d] in
+ * the input type, or NULL for no normalisation; rows below `norm_from` are rotated only
+ * (keys that come from the cache are stored normalised); freqs: float32
+ * [positions, d/2, 2] = (cos, sin) of position * theta^(-2i/d), token t uses position
+ * pos0 + t; out: [1, H, n_tok, d].  d even, <= 128.  Arithmetic in fp32 with the
+ * reference's rounding points. */
+int attn_b200_qk_norm_rope(const void* x, const void* weight, const float* freqs, void* out,
+                           int32_t n_tok, int32_t H, int32_t d, int32_t pos0, int32_t norm_from,
+                           float eps, int32_t dtype, void* stream);
+
 /* Number of kernels the last successful call of the calling thread launched. */
 int attn_b200_last_launch_count(void);
 

@@ -197,6 +197,35 @@ def closed_form_all(Q, K, V, dO, g_dQ, g_dK, g_dV, *, window_size: int, chunk_id
 
 
 # --------------------------------------------------------------------------
+# the step before attention: per-head RMS norm and rotary embedding
+# --------------------------------------------------------------------------
+def rope_freqs_cis(head_dim: int, positions: int, theta: float = 10000.0) -> torch.Tensor:
+    """complex64 [positions, head_dim/2], as reference ``e2e/ttt_pytorch/model.py:87-93``."""
+    freqs = 1.0 / (theta ** (torch.arange(0, head_dim, 2).float() / head_dim))
+    ang = torch.outer(torch.arange(positions).float(), freqs)
+    return torch.polar(torch.ones_like(ang), ang)
+
+
+def qk_norm_rope_oracle(x: torch.Tensor, weight: Optional[torch.Tensor], freqs_cis: torch.Tensor,
+                        pos0: int = 0, eps: float = 1e-6, norm_from: int = 0) -> torch.Tensor:
+    """x [n_tok, H, d] -> [1, H, n_tok, d].  RMS normalisation exactly as the reference's
+    ``RMSNorm.forward`` (``model.py:82-84``: fp32 statistics, result cast to the input type, then
+    multiplied by the weight) on rows >= ``norm_from``; rotary embedding exactly as its
+    ``apply_rotary_emb`` (``model.py:96-116``: pairs of consecutive elements as complex numbers
+    times ``freqs_cis`` in fp32, cast back); then the permutation of ``model.py:182-184``."""
+    n_tok = x.shape[0]
+    y = x
+    if weight is not None:
+        xf = x.float()
+        normed = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight.to(x.dtype)
+        y = torch.cat([x[:norm_from], normed[norm_from:]], dim=0)
+    xc = torch.view_as_complex(y.float().reshape(*y.shape[:-1], -1, 2).contiguous())
+    fc = freqs_cis[pos0:pos0 + n_tok].unsqueeze(-2)
+    out = torch.view_as_real(xc * fc).flatten(-2).to(x.dtype)
+    return out.permute(1, 0, 2).unsqueeze(0)
+
+
+# --------------------------------------------------------------------------
 # seeded inputs and error metrics
 # --------------------------------------------------------------------------
 INPUT_NAMES = ("Q", "K", "V", "dO", "g_dQ", "g_dK", "g_dV")

@@ -13,7 +13,17 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 def golden_case_names():
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
-    return [n for n in names if n != "config1_head"]
+    return [n for n in names if n != "config1_head" and not n.startswith("prep_")]
+
+
+def load_prep_golden():
+    """(meta, x bf16 [n_tok, H, d], weight bf16 [d], out fp32 [1, H, n_tok, d]) produced by the
+    reference's own RMSNorm and apply_rotary_emb."""
+    z = np.load(os.path.join(GOLDEN_DIR, "prep_qk_norm_rope.npz"))
+    n_tok, H, d, pos0, norm_from = (int(v) for v in z["meta"])
+    x = torch.from_numpy(z["x"].view(np.int16).copy()).view(torch.bfloat16)
+    w = torch.from_numpy(z["w"].view(np.int16).copy()).view(torch.bfloat16)
+    return dict(n_tok=n_tok, H=H, d=d, pos0=pos0, norm_from=norm_from), x, w, torch.from_numpy(z["out"])
 
 
 def load_golden(name):

@@ -31,11 +31,17 @@ sys.path.insert(0, os.path.join(HERE, "..", "..", "oracle"))
 from attention_oracle import INPUT_NAMES, OUTPUT_NAMES, make_inputs  # noqa: E402
 
 
-def load_reference(ref_root: str):
+def load_reference_module(ref_root: str):
     path = os.path.join(ref_root, "e2e", "ttt_pytorch", "model.py")
     spec = importlib.util.spec_from_file_location("ref_model", path)
     mod = importlib.util.module_from_spec(spec)
+    sys.modules["ref_model"] = mod          # dataclasses look their module up by name
     spec.loader.exec_module(mod)
+    return mod
+
+
+def load_reference(ref_root: str):
+    mod = load_reference_module(ref_root)
     return mod.make_sw_causal_mask, mod.reference_attention
 
 
@@ -107,6 +113,24 @@ def main():
         blob["sum_" + n] = np.array(float(out[n].double().sum()))
     np.savez_compressed(os.path.join(HERE, "config1_head.npz"), **blob)
     print("config1_head ok")
+
+    # the step before attention: the reference's own RMSNorm and apply_rotary_emb on [n_tok, H, d]
+    mod = load_reference_module(ref_root)
+    g = torch.Generator(device="cpu").manual_seed(11)
+    n_tok, H, d, pos0, norm_from = 48, 3, 64, 5, 16
+    x = torch.randn(n_tok, H, d, generator=g).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16)
+    norm = mod.RMSNorm(d, eps=1e-6).to(torch.bfloat16)
+    with torch.no_grad():
+        norm.weight.copy_(w)
+        fc = mod.precompute_freqs_cis(d, 128)
+        y = torch.cat([x[:norm_from], norm(x[norm_from:])], dim=0)
+        out = mod.apply_rotary_emb(y, fc[pos0:pos0 + n_tok]).permute(1, 0, 2).unsqueeze(0)
+    np.savez_compressed(os.path.join(HERE, "prep_qk_norm_rope.npz"),
+                        meta=np.array([n_tok, H, d, pos0, norm_from], dtype=np.int64),
+                        x=x.view(torch.int16).numpy().view(np.uint16), w=w.view(torch.int16).numpy().view(np.uint16),
+                        out=out.float().numpy())
+    print("prep_qk_norm_rope ok")
 
 
 if __name__ == "__main__":
