@@ -222,6 +222,27 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def bind_to_gpu_cpus(gpu_index: int):
+    """Restricts this process to the CPU cores next to its GPU (the driver's own affinity mask for
+    the device), so that the page-locked host buffers of the end-to-end leg are allocated on the
+    GPU's NUMA node: with eight ranks on one box the host-side copies otherwise all cross the
+    same memory controller.  Best effort; returns the number of cores kept or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        n_cpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (n_cpu + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:  # noqa: BLE001
+        pass
+    return None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -235,6 +256,7 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_cpus(local)      # before any page-locked allocation
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -366,8 +388,8 @@ def run_ours(args):
     # The (batch, head) slices are independent, so the host-buffer path is pipelined over
     # chunks of slices on three streams: upload of chunk c+1, kernels of chunk c and download
     # of chunk c-1 overlap (PCIe is full duplex).  Every byte still crosses inside the timed region.
-    # at most one chunk per slice; chunk sizes differ by at most one
-    n_chunks = max(1, min(args.e2e_chunks, bh_local))
+    # chunks of at least four slices (128 CTAs per kernel), sizes differing by at most one
+    n_chunks = max(1, min(args.e2e_chunks, bh_local // 4 if bh_local >= 4 else 1))
     chunk_bounds = [sharding.shard_range(bh_local, n_chunks, c) for c in range(n_chunks)]
     s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
 
@@ -440,7 +462,8 @@ def run_ours(args):
             "peaks": peaks, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": int(h2d) // bh_local * BH, "d2h_bytes_per_step": int(d2h) // bh_local * BH,
-                    "pipeline": f"{n_chunks} chunks of (batch, head) slices on upload / compute / download streams"},
+                    "pipeline": f"{n_chunks} chunks of (batch, head) slices on upload / compute / download streams",
+                    "cpu_cores_bound_to_gpu": numa},
             "gpu_launches": int(launches_per_step) * args.steps,
             "device_status": status,
         }

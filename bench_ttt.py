@@ -74,6 +74,9 @@ def forward_loss(cfg, slow, fast, ids, targets, attention):
     for i in range(cfg["layers"]):
         p = f"blk{i}."
         h = F.layer_norm(x, (d,), fast[p + "ln1.w"], fast[p + "ln1.b"])
+        # one GEMM for the three projections, then three 25 MB copies into the attention layout
+        # (about 10 us each at this size, under 1 % of the step; per-head GEMMs that write
+        # [B, H, N, hd] directly have N = 64 outputs and cost more than the copies they save)
         qkv = F.linear(h, fast[p + "qkv"]).view(B, N, 3, H, hd).permute(2, 0, 3, 1, 4)   # [3, B, H, N, hd]
         o = attention(qkv[0].contiguous(), qkv[1].contiguous(), qkv[2].contiguous())     # [B, H, N, hd]
         x = x + F.linear(o.transpose(1, 2).reshape(B, N, d), fast[p + "proj"])
