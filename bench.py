@@ -116,6 +116,14 @@ class ClockSampler:
                     samples=len(sm), reasons=sorted(reasons))
 
 
+def usable_cores() -> int:
+    """Cores this process may run on (its affinity mask), not the machine's total."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_path(orc):
     """The CPU implementation that is timed: the reference's own `reference_attention` and
     `make_sw_causal_mask` (e2e/ttt_pytorch/model.py, byte-compiled into oracle/_ref/ by
@@ -198,7 +206,7 @@ def run_reference(args):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import attention_oracle as orc
     w = WORKLOAD
-    torch.set_num_threads(os.cpu_count() or 1)
+    torch.set_num_threads(usable_cores())
     heads_per_step = 4
     flops_head = 2.0 * w["D"] * HVP_GEMMS * visible_pairs_causal(w["N"])
     for _ in range(args.warmup if args.warmup < 2 else 1):
@@ -514,7 +522,7 @@ def run_ours(args):
             if rk is not None:
                 line["vs_reference_kernels"] = rk
         if world == 1 and not args.no_cpu_baseline:
-            torch.set_num_threads(os.cpu_count() or 1)
+            torch.set_num_threads(usable_cores())
             n_cpu = 16
             sec, threads, kind = cpu_hvp_seconds(orc, torch, n_cpu, N, D)
             cpu_val = 2.0 * D * HVP_GEMMS * visible_pairs_causal(N) * n_cpu / sec / 1e12
