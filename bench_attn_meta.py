@@ -19,8 +19,8 @@ Two arms on the same inputs: `kernels` (this repository's `flash_attention_v7`) 
 materialises the N_q x N_kv matrices).  Reported per shape: median step time (CUDA events) and
 peak memory at batch 1, then the largest batch <= 64 whose peak memory stays within the budget
 (binary search, as the reference does) with its step time and tokens/s.  One JSON line per
-measurement.  The reference's own numbers for these rows were taken on an A100 and are quoted in
-BASELINE.md; nothing here reads them.
+measurement.  (The reference's own record of these workloads was taken on an A100, 75 000 MB
+budget; nothing here reads it.)
 """
 from __future__ import annotations
 
