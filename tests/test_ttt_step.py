@@ -20,7 +20,7 @@ def _step(cfg, dev, dtype, attention):
     loss = bt.ttt_step(cfg, slow, fast, ids, targets, attention)
     loss.backward()
     grads = {n: p.grad.detach().float().cpu() for n, p in {**slow, **fast}.items()}
-    return float(loss), grads
+    return float(loss.detach()), grads
 
 
 def test_meta_step_runs_on_cpu_with_math_attention():
