@@ -17,7 +17,9 @@ constexpr int kTmemCols = 512;
 constexpr uint32_t kAtomBytesStat = BM * 128;   // [128 rows][64 halves], 16 KB
 constexpr uint32_t kAtomBytesStrm = BN * 128;   // [ 64 rows][64 halves],  8 KB
 
-enum Kind { FWD_LSE = 0, FWD_OUT, BWD_ROW, BWD_COL, HVP_PRE, HVP_ROW, HVP_COL };
+// Kernel ids inside device status codes (the backward kernels use 18 and 19, the forward kernel
+// 20, the self-test 0x6f); the values are documented with the C ABI and do not change.
+enum Kind { HVP_PRE = 4, HVP_ROW = 5, HVP_COL = 6 };
 enum TensorId { T_Q = 0, T_K, T_V, T_dO, T_gQ, T_gK, T_gV, T_COUNT };
 
 // Output tensors by operation: forward {O}; backward {dQ, dK, dV}; double backward

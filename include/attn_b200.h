@@ -168,7 +168,11 @@ int attn_b200_last_launch_count(void);
  * has given up on a bounded wait since the last read, otherwise a code naming
  * the kernel and the wait.  Synchronises the device.  Kernels never spin
  * forever: each wait has an iteration limit, after which the kernel records its
- * code here and returns. */
+ * code here and returns.  Code = (kernel id + 1) << 8 | wait id, kernel ids:
+ * 4 / 5 / 6 double-backward scalar + g_dO / g_Q / g_K + g_V kernel, 18 / 19
+ * backward row / column kernel, 20 forward, 0x6f the primitive self-test (codes
+ * 0x7001..0x7003); wait id 15 = the launch gave the kernel less shared memory
+ * than its layout needs. */
 int attn_b200_device_status(uint32_t* code);
 
 /* Registers a page-locked host word (cudaHostAlloc / cudaHostRegister memory, mapped into
