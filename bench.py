@@ -197,6 +197,46 @@ def reference_kernels_block(torch, tcapi, orc):
     return out
 
 
+def prep_block(torch, peaks):
+    """The fused RMS-norm + rotary + layout kernel in front of the attention calls
+    (`attention_cuda.qk_norm_rope`), bf16, at the K/V stream of the reference's largest model shape
+    (16384 tokens x 32 heads x 128) and of its 125M shape (9216 x 12 x 64): device time against the
+    HBM roofline (algorithmic bytes = one read and one write of the tensor; the table of angles is
+    shared by the heads and stays in L2), and the same computation as eager PyTorch operations."""
+    sys.path.insert(0, os.path.join(ROOT, "610sample_b200"))
+    import attention_cuda
+    qk_prep = importlib.import_module("610sample_b200.qk_prep")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, (n_tok, H, d) in (("16384x32x128", (16384, 32, 128)), ("9216x12x64", (9216, 12, 64))):
+        gen = torch.Generator(device="cpu").manual_seed(0)
+        x = torch.randn(n_tok, H, d, generator=gen).to(torch.bfloat16).to(dev)
+        w = (1.0 + 0.1 * torch.randn(d, generator=gen)).to(torch.bfloat16).to(dev)
+        freqs = qk_prep.rope_table(d, n_tok, device=dev)
+
+        def med(fn, reps=20):
+            for _ in range(3):
+                fn()
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+            for a, b in evs:
+                flush.zero_()
+                a.record()
+                fn()
+                b.record()
+            torch.cuda.synchronize()
+            return statistics.median(a.elapsed_time(b) for a, b in evs)
+        ms = med(lambda: attention_cuda.qk_norm_rope(x, w, freqs, 0, 1e-6, 0))
+        eager_ms = med(lambda: qk_prep.qk_norm_rope_torch(x, w, freqs), reps=5)
+        nbytes = 2 * x.numel() * x.element_size()
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"us": ms * 1e3, "eager_torch_us": eager_ms * 1e3, "algorithmic_bytes": nbytes,
+                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                  "frac": gbs / peaks["hbm_gbs"], "traffic": None}}
+        del x, w, freqs
+    return out
+
+
 def run_reference(args):
     """CPU arm: the reference's own CPU implementation of the path on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -517,6 +557,8 @@ def run_ours(args):
                                                 "algorithmic bytes of the pass: %.0f" % ((12 * N * D * 2 + 4 * N) * BH),
                                 "peak_source": peaks["source"], "kernel_ms": phase_ms,
                                 "dominant_kernel": "hvp_" + dom, "executed": executed}
+        if world == 1 and not args.no_prep:
+            line["prep"] = prep_block(torch, peaks)
         if world == 1 and not args.no_ref_kernels:
             rk = reference_kernels_block(torch, tcapi, orc)
             if rk is not None:
@@ -547,6 +589,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the >= 2 s loop under the power cap")
     ap.add_argument("--no-ttt", action="store_true", help="skip the TTT meta-step of bench_ttt.py")
+    ap.add_argument("--no-prep", action="store_true", help="skip the timing of the fused norm + rotary kernel")
     ap.add_argument("--no-ref-kernels", action="store_true", help="skip the comparison with the reference's own CUDA kernels")
     ap.add_argument("--bh", type=int, default=0,
                     help="profiling only: number of (batch, head) slices instead of the workload's 64")

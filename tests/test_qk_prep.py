@@ -46,7 +46,11 @@ def test_kernel_matches_reference_fixture_and_oracle(prep):
     err = (got.float().cpu() - want).abs()
     assert float((err / want.abs().clamp_min(1e-3)).max()) <= 2 ** -7
     assert float((err > 0).float().mean()) < 0.02
-    for dtype, D, H, n in ((torch.float16, 128, 4, 300), (torch.float32, 80, 2, 77), (torch.bfloat16, 96, 16, 1024)):
+    # the last three: a head count that is not a multiple of the four a lane group walks over, a
+    # width of 8 lanes with a partly filled last CTA, and a head dimension (not a multiple of 8)
+    # that takes the pairwise kernel
+    for dtype, D, H, n in ((torch.float16, 128, 4, 300), (torch.float32, 80, 2, 77), (torch.bfloat16, 96, 16, 1024),
+                           (torch.float16, 64, 5, 130), (torch.bfloat16, 16, 7, 33), (torch.bfloat16, 20, 3, 65)):
         xx = torch.randn(n, H, D).to(dtype)
         ww = (1 + 0.1 * torch.randn(D)).to(dtype)
         fc = orc.rope_freqs_cis(D, n + 9)
@@ -58,6 +62,27 @@ def test_kernel_matches_reference_fixture_and_oracle(prep):
         no_norm = prep.qk_norm_rope(xx.cuda(), None, prep.rope_table(D, n + 9, device="cuda"), pos0=9)
         ref2 = orc.qk_norm_rope_oracle(xx, None, fc, pos0=9)
         assert float((no_norm.float().cpu() - ref2.float()).abs().max()) <= tol * float(ref2.float().abs().max())
+
+
+@pytest.mark.gpu
+def test_kernel_full_tile_variant_matches_oracle(prep):
+    """Shapes whose CTAs are all full and whose normalisation covers every token take the
+    guard-free variant of the kernel; the same shapes with one token more take the guarded one,
+    and the two agree bit for bit on the tokens they share."""
+    for dtype, D, H, n in ((torch.bfloat16, 128, 8, 256), (torch.float16, 64, 4, 96), (torch.float32, 128, 4, 32),
+                           (torch.bfloat16, 64, 12, 1024)):
+        xx = torch.randn(n + 1, H, D).to(dtype)
+        ww = (1 + 0.1 * torch.randn(D)).to(dtype)
+        fc = orc.rope_freqs_cis(D, n + 4)
+        table = prep.rope_table(D, n + 4, device="cuda")
+        tol = {torch.float16: 2 ** -9, torch.bfloat16: 2 ** -7, torch.float32: 1e-5}[dtype]
+        for weight in (ww, None):
+            ref = orc.qk_norm_rope_oracle(xx[:n], weight, fc, pos0=3)
+            wc = None if weight is None else weight.cuda()
+            full = prep.qk_norm_rope(xx[:n].cuda(), wc, table, pos0=3)
+            assert float(((full.float().cpu() - ref.float()).abs() / (1.0 + ref.float().abs())).max()) <= tol, (dtype, D)
+            ragged = prep.qk_norm_rope(xx.cuda(), wc, table, pos0=3)
+            assert torch.equal(ragged[:, :, :n], full), (dtype, D)
 
 
 @pytest.mark.gpu
