@@ -49,6 +49,8 @@ COL_KERNEL_GEMMS = 8
 # capture of this bench at 16 (batch, head) slices; traffic grows in proportion to the number of
 # slices, so the bench scales it by BH / 16.  To be refreshed whenever a kernel changes.
 NCU_TRAFFIC_BYTES_16_SLICES = {"pre": 193.3e6, "row": 173.6e6, "col": 137.3e6}
+# the same for one launch of the fused norm + rotary kernel (part of the output is still in L2 when it ends)
+NCU_PREP_TRAFFIC_BYTES = {"16384x32x128": 232.2e6}
 
 
 def visible_pairs_causal(n: int) -> int:
@@ -232,7 +234,7 @@ def prep_block(torch, peaks):
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[name] = {"us": ms * 1e3, "eager_torch_us": eager_ms * 1e3, "algorithmic_bytes": nbytes,
                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                  "frac": gbs / peaks["hbm_gbs"], "traffic": None}}
+                                  "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_PREP_TRAFFIC_BYTES.get(name)}}
         del x, w, freqs
     return out
 
