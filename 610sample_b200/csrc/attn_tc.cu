@@ -14,23 +14,62 @@ namespace attn {
 namespace tc {
 
 // ---------------------------------------------------------------------------
-// D_i = sum_d dO * O  (one warp per query row), used by the first backward.
-// Reference: csrc/flash_double_backward_v7.cu:721-739.
+// D_i = sum_d dO * O, used by the first backward.  Reference: csrc/flash_double_backward_v7.cu:721-739.
+// Bound by HBM traffic (one read of dO and of O): G lanes own a row, a lane eight consecutive
+// elements of it (one 16-byte load per tensor), and every lane group walks over kRowdotRows rows
+// with all its loads in flight.  D is a multiple of 16, so every 16-byte load is aligned.
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void rowdot_kernel(const T* __restrict__ a, const T* __restrict__ b, float* __restrict__ out,
-                              long long rows, int D) {
-  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (r >= rows) return;
-  const int lane = threadIdx.x & 31;
-  float acc = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    acc += Elem<T>::to_float(a[r * D + d]) * Elem<T>::to_float(b[r * D + d]);
-    acc += Elem<T>::to_float(a[r * D + d + 1]) * Elem<T>::to_float(b[r * D + d + 1]);
+constexpr int kRowdotRows = 4;
+
+template <typename T> __device__ __forceinline__ float2 widen_pair(uint32_t w);
+template <> __device__ __forceinline__ float2 widen_pair<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 widen_pair<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+template <typename T, int G>
+__global__ void __launch_bounds__(256)
+rowdot_kernel(const T* __restrict__ a, const T* __restrict__ b, float* __restrict__ out, long long rows, int D) {
+  const int sub = threadIdx.x % G;
+  const long long r0 = ((long long)blockIdx.x * (256 / G) + threadIdx.x / G) * kRowdotRows;
+  const bool lane_on = sub * 8 < D;
+  uint4 va[kRowdotRows], vb[kRowdotRows];
+#pragma unroll
+  for (int i = 0; i < kRowdotRows; ++i) {
+    va[i] = vb[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (lane_on && r0 + i < rows) {
+      va[i] = __ldg(reinterpret_cast<const uint4*>(a + (r0 + i) * D + sub * 8));
+      vb[i] = __ldg(reinterpret_cast<const uint4*>(b + (r0 + i) * D + sub * 8));
+    }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) out[r] = acc;
+  for (int i = 0; i < kRowdotRows; ++i) {
+    const uint32_t wa[4] = {va[i].x, va[i].y, va[i].z, va[i].w}, wb[4] = {vb[i].x, vb[i].y, vb[i].z, vb[i].w};
+    float acc = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 x = widen_pair<T>(wa[q]), y = widen_pair<T>(wb[q]);
+      acc = fmaf(x.x, y.x, acc);
+      acc = fmaf(x.y, y.y, acc);
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);   // every lane of the warp takes part
+    if (sub == 0 && r0 + i < rows) out[r0 + i] = acc;
+  }
+}
+
+template <typename T>
+static cudaError_t launch_rowdot(const T* a, const T* b, float* out, long long rows, int D, cudaStream_t s) {
+  const int G = D <= 32 ? 4 : D <= 64 ? 8 : 16;
+  const long long rows_per_cta = (long long)(256 / G) * kRowdotRows;
+  const long long ctas = (rows + rows_per_cta - 1) / rows_per_cta;
+  if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  if (G == 4) rowdot_kernel<T, 4><<<(unsigned)ctas, 256, 0, s>>>(a, b, out, rows, D);
+  else if (G == 8) rowdot_kernel<T, 8><<<(unsigned)ctas, 256, 0, s>>>(a, b, out, rows, D);
+  else rowdot_kernel<T, 16><<<(unsigned)ctas, 256, 0, s>>>(a, b, out, rows, D);
+  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------
@@ -321,8 +360,7 @@ static cudaError_t launch_op(int op, const TmaMaps& maps, const Geometry& g, con
   } else if (op == OP_BACKWARD) {
     const long long rows = (long long)g.BH * g.N_q;
     if (rows > 0) {
-      rowdot_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)t.dO, (const T*)t.O, t.Dv, rows, g.D);
-      e = cudaGetLastError();
+      e = launch_rowdot<T>((const T*)t.dO, (const T*)t.O, t.Dv, rows, g.D, s);
     }
     if (e == cudaSuccess)
       e = run_side_by_side(s, true,
