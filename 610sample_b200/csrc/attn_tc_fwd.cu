@@ -318,17 +318,24 @@ fwd_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_wait(s_[c]);
 
-      // scaled scores in log2 units, -inf where masked; their maximum
-      float mx = -INFINITY;
+      // maximum of the raw scores (-inf where masked) in eight independent chains; the scale
+      // (positive) is applied to the maximum here and to the scores inside the exponent's fma
+      if (masked) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float x = __uint_as_float(s_[c][e]) * g.scale_log2e;
-          if (masked) x = ((uint32_t)(j0 + 16 * c + e - vlo) < vspan) ? x : -INFINITY;
-          s_[c][e] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
+          for (int e = 0; e < 16; ++e)
+            if (!((uint32_t)(j0 + 16 * c + e - vlo) < vspan)) s_[c][e] = 0xff800000u;   // -inf
+      }
+      float mx8[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(__uint_as_float(s_[0][e]), __uint_as_float(s_[0][8 + e]));
+#pragma unroll
+      for (int c = 1; c < 4; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], fmaxf(__uint_as_float(s_[c][e]), __uint_as_float(s_[c][8 + e])));
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) *
+                       g.scale_log2e;
       // lazy rescale: the reference moves only when this tile exceeds it by more than kTau
       const bool grow = mx > m_ref + kTau || (m_ref == -INFINITY && mx > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
@@ -361,19 +368,24 @@ fwd_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors
         }
       }
       const float nm = (m_ref == -INFINITY) ? 0.f : -m_ref;    // no visible key yet: every p below is masked to 0
-      float sum0 = 0.f, sum1 = 0.f;
+      const float2 sc2 = make_float2(g.scale_log2e, g.scale_log2e), nm2 = make_float2(nm, nm);
+      float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t kp[8];
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float p0 = ex2(__uint_as_float(s_[c][e]) + nm), p1 = ex2(__uint_as_float(s_[c][e + 1]) + nm);
-          sum0 += p0; sum1 += p1;
-          kp[e >> 1] = Pack<T>::pack(p0, p1);
+        for (int e = 0; e < 16; e += 4) {
+          const float2 xa = __ffma2_rn(make_float2(__uint_as_float(s_[c][e]), __uint_as_float(s_[c][e + 1])), sc2, nm2);
+          const float2 xb = __ffma2_rn(make_float2(__uint_as_float(s_[c][e + 2]), __uint_as_float(s_[c][e + 3])), sc2, nm2);
+          const float2 pa = make_float2(ex2(xa.x), ex2(xa.y)), pb = make_float2(ex2(xb.x), ex2(xb.y));
+          sum_a = __fadd2_rn(sum_a, pa);
+          sum_b = __fadd2_rn(sum_b, pb);
+          kp[e >> 1] = Pack<T>::pack(pa.x, pa.y);
+          kp[(e >> 1) + 1] = Pack<T>::pack(pb.x, pb.y);
         }
         tmem_st8(sbuf + 8 * c, kp);      // over score columns this thread has read
       }
-      l_sum += sum0 + sum1;
+      l_sum += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
