@@ -15,8 +15,16 @@
 // score columns they have read; the output products take them from there as their A operand.
 // BWD_COL computes transposed scores (keys on the TMEM lanes) so that operand roles are the same
 // as in the row kind; its per-query scalars (L, Dv) are staged in shared memory per tile.
-// One warp issues every MMA, each batch by one elected lane inside a single branch; with two
-// buffers per region the score products of the row kind run two tiles ahead.  Head dimensions
+// Two warps issue the MMAs, each batch by one elected lane inside a single branch: one the score
+// products S (a region is free again as soon as its scores are in the math warps' registers), the
+// other the outputs of a tile followed by the dP products that overwrite their operands (its own
+// program order is the only ordering needed).  In the row kind the eight math warps form two
+// groups of four that take alternate tiles (= alternate buffers of the two regions), a thread
+// owning a whole row of its tile, so that one group computes while the other waits for its
+// products or for tensor-memory reads (clock stamps: tile period 1 479 -> 1 281 clk with the
+// groups alone, the issuing warp then being the limit; with the second issuing warp the row
+// kernel takes 368 instead of 408 us at B4 H16 N4096 D128).  The column kind has no room for
+// second buffers at D = 128 and keeps all eight warps on one tile.  Head dimensions
 // below the tile width run zero-padded (TMA fills the padding) with the padding k-steps and
 // columns skipped.  Result tiles leave through shared memory and TMA stores.
 // (The forward pass is in attn_tc_fwd.cu.)
@@ -30,7 +38,7 @@ namespace tc {
 enum FbKind { FB_BWD_ROW = 2, FB_BWD_COL = 3 };   // numbering of launch_fwd_bwd
 
 constexpr int kFbMmaWarp = 9;
-constexpr int kFbThreads = 320;
+constexpr int kFbThreads = 352;    // 8 math warps, TMA producer, two MMA issuers
 constexpr int kFbMaxStages = 8;
 
 struct FbControl {
@@ -41,7 +49,7 @@ struct FbControl {
   uint64_t ra_full[2];
   uint64_t rb_full[2];
   uint64_t op_full[2];       // math warps are done with the regions of a tile (operands written)
-  uint64_t ra_free;          // BWD_COL only: RA has been read (before the tile is finished)
+  uint64_t ra_free[2];       // the scores of a tile are in the math warps' registers
   uint64_t acc_done;
   uint64_t stats_ready[2];
   uint32_t tmem_base;
@@ -121,7 +129,8 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
   const int n_iter = (hi > lo) ? ((hi + BN - 1) / BN - t_begin) : 0;
 
   const uint32_t bar_staging_full = smem_u32(&ctl->staging_full), bar_stat_ready = smem_u32(&ctl->stat_ready);
-  const uint32_t bar_ra_free = smem_u32(&ctl->ra_free), bar_acc_done = smem_u32(&ctl->acc_done);
+  const uint32_t bar_acc_done = smem_u32(&ctl->acc_done);
+  auto bar_ra_free = [&](int b) { return smem_u32(&ctl->ra_free[b]); };
   auto bar_stream_full = [&](int s) { return smem_u32(&ctl->stream_full[s]); };
   auto bar_stream_empty = [&](int s) { return smem_u32(&ctl->stream_empty[s]); };
   auto bar_ra_full = [&](int b) { return smem_u32(&ctl->ra_full[b]); };
@@ -138,10 +147,11 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_ra_full(b), 1);
       mbar_init(bar_rb_full(b), 1);
-      mbar_init(bar_op_full(b), kMathWarps);
+      // row kind: a tile belongs to one group of four math warps
+      mbar_init(bar_op_full(b), CF::kCol ? kMathWarps : kMathWarps / 2);
+      mbar_init(bar_ra_free(b), CF::kCol ? kMathWarps : kMathWarps / 2);
       mbar_init(smem_u32(&ctl->stats_ready[b]), kMathWarps);
     }
-    mbar_init(bar_ra_free, kMathWarps);
     mbar_init(bar_acc_done, 1);
     ctl->abort_flag = 0u;
     ctl->tmem_base = 0u;
@@ -194,7 +204,7 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
   // =========================================================================
   // MMA issuer (converged warp, one elected lane issues)
   // =========================================================================
-  else if (warp == kFbMmaWarp) {
+  else if (warp == kFbMmaWarp || warp == kFbMmaWarp + 1) {
     if (n_iter > 0) {
       bool ok = mbar_wait(bar_stat_ready, 0, abort_flag, t.status, wait_code(KCODE, 2));
       ok = __all_sync(0xffffffffu, ok);
@@ -262,47 +272,44 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
         __syncwarp();
       };
 
-      // score products run kBufs tiles ahead of the math warps
-      for (int i = 0; i < kBufs && i < n_iter && ok; ++i) {
-        ok = wait_stream(i);
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_ra(i);
-        issue_rb(i);
-      }
-      for (int j = 0; j < n_iter && ok; ++j) {
-        const int b = j % kBufs;
-        if constexpr (CF::kCol) {
-          // single-buffered regions: S^T of the next tile as soon as this tile's has been read
-          if (j + 1 < n_iter) {
-            ok = wait_stream(j + 1);
-            if (ok) ok = mbar_wait(bar_ra_free, j & 1, abort_flag, t.status, wait_code(KCODE, 4));
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_ra(j + 1);
-          }
+      // Two barriers in one round: the even lanes wait for the first, the odd lanes for the second
+      auto wait_two = [&](uint32_t bar0, uint32_t par0, int id0, bool has1, uint32_t bar1, uint32_t par1, int id1) {
+        const bool second = has1 && (lane & 1);
+        bool w = mbar_wait(second ? bar1 : bar0, second ? par1 : par0, abort_flag, t.status, wait_code(KCODE, second ? id1 : id0));
+        return (bool)__all_sync(0xffffffffu, w);
+      };
+      if (warp == kFbMmaWarp) {
+        // ---- first warp: the score products, as soon as the region's previous scores have been read
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int b = j % kBufs;
+          ok = wait_two(bar_stream_full(j % CF::kStages), (j / CF::kStages) & 1, 3,
+                        j >= kBufs, bar_ra_free(b), ((j / kBufs) & 1) ^ 1, 4);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_ra(j);
         }
-        ok = mbar_wait(bar_op_full(b), (j / kBufs) & 1, abort_flag, t.status, wait_code(KCODE, 5));
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_out(j);
-        commit(bar_stream_empty(j % CF::kStages));    // every product reading this stage has been issued
-        const int nj = j + kBufs;
-        if (nj < n_iter) {
-          if constexpr (CF::kCol) {
-            issue_rb(nj);                           // after the outputs that read RB (in order)
-          } else {
-            ok = wait_stream(nj);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_ra(nj);                           // buffer b: read by tile j, its outputs issued above
-            issue_rb(nj);
-          }
+      } else {
+        // ---- second warp: outputs of a tile, then the dP products that overwrite their operands
+        for (int i = 0; i < kBufs && i < n_iter && ok; ++i) {
+          ok = wait_stream(i);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_rb(i);
         }
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int b = j % kBufs, nj = j + kBufs;
+          ok = wait_two(bar_op_full(b), (j / kBufs) & 1, 5,
+                        nj < n_iter, bar_stream_full(nj % CF::kStages), (nj / CF::kStages) & 1, 3);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_out(j);
+          // every product reading this stage has been issued (the score product of the tile, issued by
+          // the first warp, completed before the math warps could write the operands waited for above)
+          commit(bar_stream_empty(j % CF::kStages));
+          if (nj < n_iter) issue_rb(nj);
+        }
+        if (ok) commit(bar_acc_done);
       }
-      if (ok) commit(bar_acc_done);
     }
   }
   // =========================================================================
@@ -388,6 +395,79 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
     };
     if constexpr (CF::kCol) { if (n_iter > 0) publish_stat(0, fetch_stat(0)); }
 
+    if constexpr (!CF::kCol) {
+      // ---- row kind: the eight math warps form two groups of four; group w takes the tiles of
+      // parity w (= score buffer w), a thread its whole row of the tile (64 scores).  While one
+      // group waits for its products or for tensor-memory reads, the other one computes.
+      const int grp = half;
+      for (int it = grp; it < n_iter && ok; it += 2) {
+        const int b = it & 1;
+        const int j0 = (t_begin + it) * BN;
+        const bool masked = !(j0 >= vlo && j0 + BN - 1 < vhi);
+        const uint32_t ra = lane_addr + CF::kRA + 64 * b;
+        const uint32_t rb = lane_addr + CF::kRB + 64 * b;
+        ok = mbar_wait(bar_ra_full(b), (it >> 1) & 1, abort_flag, t.status, wait_code(KCODE, 7));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        float2 pw[32];                               // p of the whole row, carried from S to dP
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t s_[2][16];
+          tmem_ld16(ra + hh * 32, s_[0]);
+          tmem_ld16(ra + hh * 32 + 16, s_[1]);
+          tmem_ld_wait(s_[0]);
+          tmem_ld_wait(s_[1]);
+          if (hh == 1) {       // the whole row is in registers: the score product of tile it + 2 may overwrite the buffer
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_ra_free(b));
+          }
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+            for (int e = 0; e < 16; e += 2) {
+              const int cc = hh * 32 + ch * 16 + e;
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(s_[ch][e]), __uint_as_float(s_[ch][e + 1])), sl2, nL2);
+              float2 pp = make_float2(ex2(x.x), ex2(x.y));
+              if (masked) {
+                pp.x = ((uint32_t)(j0 + cc - vlo) < vspan) ? pp.x : 0.f;
+                pp.y = ((uint32_t)(j0 + cc + 1 - vlo) < vspan) ? pp.y : 0.f;
+              }
+              pw[hh * 16 + ch * 8 + (e >> 1)] = pp;
+            }
+        }
+        ok = mbar_wait(bar_rb_full(b), (it >> 1) & 1, abort_flag, t.status, wait_code(KCODE, 8));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t d_[2][16];
+          tmem_ld16(rb + hh * 32, d_[0]);
+          tmem_ld16(rb + hh * 32 + 16, d_[1]);
+          tmem_ld_wait(d_[0]);
+          tmem_ld_wait(d_[1]);
+          uint32_t kds[2][8];
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+            for (int e = 0; e < 16; e += 2) {
+              const float2 dpd = __fadd2_rn(make_float2(__uint_as_float(d_[ch][e]), __uint_as_float(d_[ch][e + 1])), nDv);
+              const float2 ds = __fmul2_rn(pw[hh * 16 + ch * 8 + (e >> 1)], dpd);
+              kds[ch][e >> 1] = Pack<T>::pack(ds.x, ds.y);
+            }
+          // dS over the dP columns this thread has just read (the layout the output product expects:
+          // 16 elements of k-step ks in 8 columns at 32 * (ks / 2) + 8 * (ks % 2))
+          tmem_st8(rb + hh * 32, kds[0]);
+          tmem_st8(rb + hh * 32 + 8, kds[1]);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_op_full(b));
+      }
+    } else
     for (int it = 0; it < n_iter && ok; ++it) {
       const int b = it % kBufs;
       const int j0 = (t_begin + it) * BN;
@@ -415,11 +495,9 @@ fb_kernel(const __grid_constant__ TmaMaps maps, const Geometry g, const Tensors 
       tmem_ld16(ra + 16, s_[1]);
       tmem_ld_wait(s_[0]);
       tmem_ld_wait(s_[1]);
-      if constexpr (CF::kCol) {
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_ra_free);
-      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ra_free(b));
       {
         uint32_t kp[2][8];
 #pragma unroll
