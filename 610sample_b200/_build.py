@@ -86,7 +86,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     for p in procs:
         if p.wait() != 0:
             raise RuntimeError("nvcc failed")
-    _run([_nvcc(), "-shared", "-o", LIB] + objs, verbose)
+    _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB] + objs, verbose)
     _write_stamp("lib.stamp", digest)
     return LIB
 
